@@ -1,0 +1,116 @@
+/* C ABI of libb200dl.so: hand-written sm_100a (B200) kernels for the two dense-contraction
+ * hot paths of HugeOrca/sm120-dl, the BF16 GEMM C = A * B^T and the FP16 FlashAttention
+ * forward.  Plain pointers and sizes only; every pointer to matrix or tensor data is a
+ * DEVICE pointer on the CUDA device that is current when the call is made; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream).
+ *
+ * All entry points return 0 on success and a negative B200_E* code on failure; the
+ * message of the most recent failure on the calling thread is b200_last_error().
+ * Launches are asynchronous on `stream`.  There is no CPU fallback: without an sm_100
+ * device the compute entry points fail with B200_ENODEVICE.
+ *
+ * Each declaration cites the reference interface (path inside HugeOrca/sm120-dl) it
+ * stands in for.
+ */
+#ifndef B200DL_H_
+#define B200DL_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)     /* bad argument: null pointer, unknown config, bad stride      */
+#define B200_ESHAPE (-2)     /* shape not supported by the chosen config (divisibility etc.) */
+#define B200_ECUDA (-3)      /* a CUDA runtime/driver call failed (sticky error stays set)  */
+#define B200_ENODEVICE (-4)  /* current device is not compute capability 10.x               */
+#define B200_EDEVICE (-5)    /* a kernel gave up a bounded wait (see b200_device_status)    */
+
+/* ------------------------------------------------------------------ GEMM config registry
+ * Replaces the generated table `kGemmConfigs[] / kGemmConfigCount` and the per-config
+ * explicit instantiations of gemm_tn<> (gemm/gemm_config_registry.hpp.in:11-37,
+ * gemm/gemm_config_registry.cu.in:6-10, gemm/gemm.cu.in:59-66).  A problem is legal for a
+ * config when M % bm == 0, N % bn == 0 and K % bk == 0 (gemm/test.cpp:449-451). */
+typedef struct b200_gemm_config {
+    const char* name;   /* unique, e.g. "bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8"            */
+    int bm;             /* output tile rows per CTA group (128 * cta_group)                  */
+    int bn;             /* output tile columns = N of one tcgen05.mma                        */
+    int bk;             /* K extent of one pipeline stage (64 elements = one 128B swizzle)   */
+    int stages;         /* depth of the TMA -> MMA shared-memory ring                        */
+    int cta_group;      /* 1 = single-CTA MMA, 2 = CTA-pair MMA (cluster of 2 along M)       */
+    int acc_bufs;       /* tensor-memory accumulator buffers (2 = epilogue overlaps mainloop) */
+    int bs_w;           /* raster: N-tiles per strip, M-major inside a strip                 */
+    int smem_bytes;     /* dynamic shared memory per CTA                                     */
+    int tmem_cols;      /* tensor-memory columns allocated per CTA                           */
+} b200_gemm_config;
+
+int b200_gemm_num_configs(void);
+/* NULL when idx is out of range. */
+const b200_gemm_config* b200_gemm_get_config(int idx);
+/* Index of the config with exactly this name, or -1. */
+int b200_gemm_find_config(const char* name);
+/* Index of the config this library would pick for the shape (largest legal tile that
+ * still fills the GPU), or -1 when no built config divides the shape. */
+int b200_gemm_default_config(int M, int N, int K);
+
+/* C[M,N] = A[M,K] * B[N,K]^T, bf16 operands, fp32 accumulation, bf16 round-to-nearest-even
+ * output, C fully overwritten (alpha = 1, beta = 0).  Row-major with leading dimensions
+ * lda, ldb, ldc in ELEMENTS (each a multiple of 8; the reference has none and means
+ * lda = ldb = K, ldc = N).  Replaces gemm_tn<T,BM,BN,BK,STAGE,CWG,WARPS_M,WARPS_N,BS_W>
+ * (gemm/gemm_cute.hpp:268-356) and the kernel b16_gemm (gemm/gemm_cute.hpp:64-266); the
+ * leading dimensions exist so an N-column shard can write its slab of a full-width C. */
+int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                      int64_t ldb, void* C, int64_t ldc, void* stream);
+
+/* ------------------------------------------------------------- attention config registry
+ * Replaces `kFlashFwdConfigs[] / kFlashFwdConfigCount / kFlashFwdDefaultConfigName`
+ * (flashattention/v3_mMnNkN/pybind/flash_fwd_config_registry.hpp.in:7-30). */
+typedef struct b200_fa_config {
+    const char* name;   /* unique, e.g. "hd128_bm64_bn64_tq128x2_tk128_s3"                   */
+    int head_dim;       /* 64 or 128                                                         */
+    int block_m;        /* seq_len must be a multiple of this (query side)                   */
+    int block_n;        /* seq_len must be a multiple of this (key side)                     */
+    int tile_q;         /* query rows per MMA tile (128)                                     */
+    int q_tiles;        /* query tiles processed concurrently by one CTA                     */
+    int tile_kv;        /* key/value rows per pipeline stage                                 */
+    int stages;         /* depth of the K/V shared-memory ring                               */
+    int nwarps;         /* warps per CTA                                                     */
+    int smem_bytes;     /* dynamic shared memory per CTA                                     */
+} b200_fa_config;
+
+int b200_fa_num_configs(void);
+const b200_fa_config* b200_fa_get_config(int idx);
+int b200_fa_find_config(const char* name);
+/* Default config for a head dimension (what fwd() uses), or -1. */
+int b200_fa_default_config(int head_dim);
+
+/* O = softmax(Q K^T * softmax_scale [+ causal mask]) V per (batch, head); fp16 in, fp32
+ * scores / softmax state / accumulation, fp16 round-to-nearest output.  Tensors are indexed
+ * [batch, seq, head, dim] through element strides {stride_b, stride_s, stride_h}; the dim
+ * stride is 1; every stride is a multiple of 8 elements.  Causal rule: key j is masked for
+ * query i when i < j (top-left aligned, seq_q == seq_k required when causal).
+ * Replaces flash_fwd<T,is_causal,H,D,bm,bn,wm,wn,STAGE>
+ * (flashattention/v3_mMnNkN/flashatten_v3.hpp:536-573), the kernel flash_atten_v3_fwd
+ * (:390-534) and run_flash_fwd_<cfg> (pybind/flash_fwd_config.cu.in:59-91).  The strides
+ * exist so a head shard can address its slice of a full [B,S,H,D] tensor. */
+int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, void* o, int batch,
+                     int seq_q, int seq_k, int heads, int head_dim, const int64_t q_strides[3],
+                     const int64_t k_strides[3], const int64_t v_strides[3],
+                     const int64_t o_strides[3], float softmax_scale, int causal, void* stream);
+
+/* ----------------------------------------------------------------------------- diagnostics */
+/* Message of the last failed call on this thread ("" if none). */
+const char* b200_last_error(void);
+/* Synchronises the current device and reads (then clears) its kernel status word: 0 when
+ * every kernel ran to completion, otherwise the code of the first bounded wait that gave
+ * up.  Returns B200_OK / B200_ECUDA. */
+int b200_device_status(uint32_t* code);
+/* Library version string. */
+const char* b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DL_H_ */

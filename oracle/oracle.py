@@ -1,0 +1,213 @@
+"""Python face of the CPU oracle.  TEST INFRASTRUCTURE ONLY.
+
+Only tests/, the smoke check and the cpu_baseline / reference legs of bench.py may import
+this module; the product package never does.
+
+Two layers:
+  * `gemm_f64`, `attention_f32`, `compare`: ctypes calls into liboracle.so (oracle.cpp,
+    OpenMP), usable at the benchmark's full sizes or on row subsets of them;
+  * `gemm_numpy`, `attention_numpy`: independent numpy float64 restatements used to pin
+    the C++ code on small cases.
+
+Parity status: "parity unpinned" with respect to reference-held vectors -- the reference
+(HugeOrca/sm120-dl) stores none; its checks are run-time comparisons against cuBLAS
+(gemm/test.cpp:394-420) and flash-attn (flashattention/v3_mMnNkN/verify.py:129).  The
+oracle is pinned to numpy float64 / torch CPU results through tests/golden/.
+
+Semantics restated (reference file:line):
+  GEMM       C = A @ B.T with A [M,K], B [N,K] (gemm/gemm_cute.hpp:302-304)
+  attention  softmax(Q K^T / sqrt(D)) V on [B,S,H,D] (kernel_traits.hpp:146-160,
+             pybind/flash_fwd_config.cu.in:27), causal mask row < col
+             (flashatten_v3.hpp:101-103)
+  compare    |got-ref| <= abs + rel*|ref| (gemm/test.cpp:165-230; verify.py:64-80)
+"""
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "liboracle.so")
+_lib = None
+
+
+def build(force=False):
+    """Compile liboracle.so with the Makefile beside this file."""
+    if force or not os.path.exists(_LIB_PATH) or (
+            os.path.getmtime(_LIB_PATH) < os.path.getmtime(os.path.join(_HERE, "oracle.cpp"))):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _LIB_PATH
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_LIB_PATH):
+            build()
+        L = ctypes.CDLL(_LIB_PATH)
+        i64p = ctypes.POINTER(ctypes.c_int64)
+        L.oracle_num_threads.restype = ctypes.c_int
+        L.oracle_gemm_bf16_tn_f64.restype = None
+        L.oracle_gemm_bf16_tn_f64.argtypes = [
+            ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_int,
+            ctypes.c_int]
+        L.oracle_fa_fwd_f32.restype = None
+        L.oracle_fa_fwd_f32.argtypes = [
+            ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+            ctypes.c_void_p, i64p, ctypes.c_void_p, i64p, ctypes.c_void_p, i64p,
+            ctypes.c_float, ctypes.c_int, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        L.oracle_compare.restype = ctypes.c_int64
+        L.oracle_compare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                     ctypes.c_double, ctypes.c_double, ctypes.c_void_p]
+        _lib = L
+    return _lib
+
+
+def num_threads():
+    return int(lib().oracle_num_threads())
+
+
+# ------------------------------------------------------------------ bit-pattern helpers
+def bf16_bits_from_f32(x):
+    """float32 array -> uint16 bf16 bit patterns, round-to-nearest-even."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = x.view(np.uint32).astype(np.uint64)
+    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
+    return rounded.astype(np.uint16)
+
+
+def f32_from_bf16_bits(b):
+    b = np.ascontiguousarray(b, dtype=np.uint16)
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+def f16_bits(x):
+    return np.ascontiguousarray(x, dtype=np.float16).view(np.uint16)
+
+
+# ------------------------------------------------------------------------ C++ oracle
+def gemm_f64(a_bits, b_bits, row_begin=0, row_count=None):
+    """a_bits [M,K], b_bits [N,K] uint16 bf16 patterns -> float64 [row_count, N]."""
+    a_bits = np.ascontiguousarray(a_bits, dtype=np.uint16)
+    b_bits = np.ascontiguousarray(b_bits, dtype=np.uint16)
+    M, K = a_bits.shape
+    N, K2 = b_bits.shape
+    assert K == K2
+    if row_count is None:
+        row_count = M - row_begin
+    assert 0 <= row_begin and row_begin + row_count <= M
+    out = np.empty((row_count, N), dtype=np.float64)
+    lib().oracle_gemm_bf16_tn_f64(M, N, K, a_bits.ctypes.data, K, b_bits.ctypes.data, K,
+                                  out.ctypes.data, N, row_begin, row_count)
+    return out
+
+
+def _strides3(t):
+    s = [st // t.itemsize for st in t.strides]
+    assert s[3] == 1, "dim stride must be 1"
+    return (ctypes.c_int64 * 3)(s[0], s[1], s[2])
+
+
+def attention_f32(q_bits, k_bits, v_bits, causal=False, scale=None, rows=None):
+    """q/k/v [B,S,H,D] uint16 fp16 patterns -> float32 [B, n_rows, H, D]."""
+    B, Sq, H, D = q_bits.shape
+    Sk = k_bits.shape[1]
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    if rows is not None:
+        rows = np.ascontiguousarray(rows, dtype=np.int32)
+        n_rows = len(rows)
+        rows_ptr = rows.ctypes.data
+    else:
+        n_rows = Sq
+        rows_ptr = None
+    out = np.empty((B, n_rows, H, D), dtype=np.float32)
+    lib().oracle_fa_fwd_f32(B, Sq, Sk, H, D, q_bits.ctypes.data, _strides3(q_bits),
+                            k_bits.ctypes.data, _strides3(k_bits), v_bits.ctypes.data,
+                            _strides3(v_bits), float(scale), int(bool(causal)), rows_ptr,
+                            n_rows, out.ctypes.data)
+    return out
+
+
+def compare(got, ref, abs_tol, rel_tol):
+    """Reference-style comparison.  Returns a dict of error statistics."""
+    got = np.ascontiguousarray(got, dtype=np.float64).ravel()
+    ref = np.ascontiguousarray(ref, dtype=np.float64).ravel()
+    assert got.shape == ref.shape
+    stats = np.zeros(6, dtype=np.float64)
+    bad = lib().oracle_compare(got.ctypes.data, ref.ctypes.data, got.size, float(abs_tol),
+                               float(rel_tol), stats.ctypes.data)
+    return {
+        "mismatches": int(bad), "count": int(got.size), "passed": bad == 0,
+        "max_abs": float(stats[0]), "max_rel": float(stats[1]), "first_bad": int(stats[2]),
+        "max_ref": float(stats[3]), "rms_ref": float(stats[4]),
+        # |diff| / max(|ref_i|, rms(ref)): relative error that stays bounded where ref ~ 0
+        "max_rel_bounded": float(stats[5]),
+    }
+
+
+# --------------------------------------------------------------------- numpy restatement
+def gemm_numpy(a_bits, b_bits):
+    a = f32_from_bf16_bits(a_bits).astype(np.float64)
+    b = f32_from_bf16_bits(b_bits).astype(np.float64)
+    return a @ b.T
+
+
+def attention_numpy(q_bits, k_bits, v_bits, causal=False, scale=None):
+    q = q_bits.view(np.float16).astype(np.float64)
+    k = k_bits.view(np.float16).astype(np.float64)
+    v = v_bits.view(np.float16).astype(np.float64)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    if scale is None:
+        scale = 1.0 / np.sqrt(D)
+    s = np.einsum("bihd,bjhd->bhij", q, k) * scale
+    if causal:
+        i = np.arange(Sq)[:, None]
+        j = np.arange(Sk)[None, :]
+        s = np.where(i < j, -np.inf, s)
+    s = s - s.max(axis=-1, keepdims=True)
+    p = np.exp(s)
+    p /= p.sum(axis=-1, keepdims=True)
+    return np.einsum("bhij,bjhd->bihd", p, v)
+
+
+# ------------------------------------------------------------------------ seeded inputs
+def make_gemm_inputs(M, N, K, seed, dist="normal_over_sqrt_k"):
+    """Deterministic bf16 operands as uint16 bit patterns, A first then B (the reference
+    fills A, B, C in that order: gemm/test.cpp:384-386).
+
+    dist: "uniform1" = uniform[-1,1) (512^3 case), "uniform01" = uniform[-0.1,0.1) (the
+    reference harness, gemm/test.cpp:384-386), "normal_over_sqrt_k" = N(0,1)/sqrt(K).
+    Generator: numpy PCG64(seed), float32 draws rounded to bf16.
+    """
+    rng = np.random.Generator(np.random.PCG64(seed))
+
+    def draw(rows):
+        if dist == "uniform1":
+            x = rng.uniform(-1.0, 1.0, size=(rows, K)).astype(np.float32)
+        elif dist == "uniform01":
+            x = rng.uniform(-0.1, 0.1, size=(rows, K)).astype(np.float32)
+        elif dist == "normal_over_sqrt_k":
+            x = rng.standard_normal(size=(rows, K), dtype=np.float32) / np.float32(np.sqrt(K))
+        else:
+            raise ValueError(dist)
+        return bf16_bits_from_f32(x)
+
+    a = draw(M)
+    b = draw(N)
+    return a, b
+
+
+def make_fa_inputs(B, S, H, D, seed, std=1.0):
+    """Deterministic fp16 q, k, v (in that order, verify.py:58-60) as uint16 patterns."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for _ in range(3):
+        x = rng.standard_normal(size=(B, S, H, D), dtype=np.float32) * np.float32(std)
+        out.append(f16_bits(x))
+    return tuple(out)

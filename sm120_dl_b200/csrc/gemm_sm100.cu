@@ -1,0 +1,455 @@
+// BF16 GEMM  C[M,N] = A[M,K] * B[N,K]^T  for sm_100a, and its C ABI.
+//
+// Same contract as the reference's gemm_tn / b16_gemm (gemm/gemm_cute.hpp:64-356): both
+// operands K-major ("TN"), fp32 accumulation, bf16 round-to-nearest-even output, C fully
+// overwritten, persistent CTAs walking a strip-rasterised tile list
+// (utils/tools.h:30-40).  Everything below that contract is new:
+//
+//   warp 0  (1 thread)  TMA producer: A and B k-blocks -> STAGES-deep shared-memory ring
+//   warp 1  (1 thread)  issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32) from the
+//                       128B-swizzled ring into a tensor-memory accumulator; with
+//                       CTA_GROUP = 2 one instruction spans the CTA pair: 256 x BN x 16,
+//                       A rows and B rows split across the two CTAs' shared memory
+//   warps 2-5           epilogue: tcgen05.ld -> fp32->bf16 -> swizzled smem -> TMA store,
+//                       one 32-row x 64-column box per warp per step, double-buffered,
+//                       overlapping the next tile's mainloop through ACC_BUFS accumulators
+//
+// Shared-memory ring slots are released by tcgen05.commit onto the leader CTA's "empty"
+// barriers; the leader's producer relays each release to the peer CTA with a remote
+// mbarrier arrive, so no multicast form of any instruction is used.
+#include <cstdio>
+#include <cstring>
+
+#include "ptx_sm100.cuh"
+#include "runtime.h"
+
+namespace b200 {
+namespace {
+
+constexpr int kBK = 64;                    // elements per k-block = one 128-byte swizzle row
+constexpr int kCtaM = 128;                 // accumulator rows per CTA = tensor-memory lanes
+constexpr int kAStageBytes = kCtaM * 128;  // 16 KiB
+constexpr int kEpiWarps = 4;
+constexpr int kEpiBoxRows = 32;
+constexpr int kEpiBoxBytes = kEpiBoxRows * 128;  // 4 KiB: 32 rows x 64 bf16
+constexpr int kThreads = 32 * (2 + kEpiWarps);
+
+constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
+
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+struct GemmTraits {
+    static constexpr int kBRows = BN / CTA_GROUP;        // B rows this CTA loads per stage
+    static constexpr int kBStageBytes = kBRows * 128;
+    static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+    static constexpr int kRingBytes = STAGES * kStageBytes;
+    static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBoxBytes;
+    static constexpr int kBarrierBytes = (2 * STAGES + 2 * ACC_BUFS) * 8 + 16;
+    // +1024: the dynamic segment is only guaranteed 16-byte aligned; the ring needs 1024.
+    static constexpr int kSmemBytes = kRingBytes + kEpiBytes + kBarrierBytes + 1024;
+    static constexpr int kTmemCols = tmem_cols_for(ACC_BUFS * BN);
+    static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
+    static_assert(ACC_BUFS * BN <= 512, "accumulators exceed the 512 tensor-memory columns");
+    static_assert(CTA_GROUP == 1 || CTA_GROUP == 2, "CTA_GROUP must be 1 or 2");
+    static_assert(kBRows % 8 == 0, "B rows per CTA must be a multiple of the 8-row swizzle group");
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB shared-memory limit of sm_100");
+};
+
+// tile id -> (tile row, tile column): N-tiles grouped in strips of bs_w, inside a strip the
+// column index moves fastest, so concurrently running CTAs share A rows and B rows in L2.
+__device__ __forceinline__ void tile_coord(int tile, int tiles_m, int tiles_n, int bs_w, int& tm,
+                                           int& tn) {
+    const int strip_tiles = bs_w * tiles_m;
+    const int strip = tile / strip_tiles;
+    const int n0 = strip * bs_w;
+    const int w = min(bs_w, tiles_n - n0);
+    const int r = tile - strip * strip_tiles;
+    tm = r / w;
+    tn = n0 + r - tm * w;
+}
+
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, int M, int N, int K, int bs_w,
+                    uint32_t* status) {
+    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
+    constexpr int BM = kCtaM * CTA_GROUP;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t ring_a = smem_base;
+    const uint32_t ring_b = smem_base + STAGES * kAStageBytes;
+    const uint32_t epi_base = smem_base + T::kRingBytes;
+    const uint32_t bar_base = epi_base + T::kEpiBytes;
+    const uint32_t full_bar = bar_base;                      // [STAGES] TMA -> MMA
+    const uint32_t empty_bar = full_bar + STAGES * 8;        // [STAGES] MMA -> TMA
+    const uint32_t accfull_bar = empty_bar + STAGES * 8;     // [ACC_BUFS] MMA -> epilogue
+    const uint32_t accempty_bar = accfull_bar + ACC_BUFS * 8;  // [ACC_BUFS] epilogue -> MMA
+    const uint32_t tmem_slot = accempty_bar + ACC_BUFS * 8;
+    const uint32_t abort_slot = tmem_slot + 4;
+    // generic pointers to the two scalar slots
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
+    volatile uint32_t* abort_ptr =
+        reinterpret_cast<volatile uint32_t*>(smem_aligned + (abort_slot - smem_base));
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta_rank = (CTA_GROUP == 2) ? cluster_ctarank() : 0u;
+    const bool is_leader = (cta_rank == 0);
+    const WaitGuard guard{abort_ptr, status};
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        for (int b = 0; b < ACC_BUFS; ++b) {
+            mbar_init(accfull_bar + 8 * b, 1);
+            mbar_init(accempty_bar + 8 * b, kEpiWarps * CTA_GROUP);
+        }
+        *abort_ptr = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+        prefetch_tensormap(&tmap_c);
+    }
+    if (warp == 1) {
+        tmem_alloc<CTA_GROUP>(tmem_slot, T::kTmemCols);
+        tmem_relinquish<CTA_GROUP>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    const int tiles_m = M / BM;
+    const int tiles_n = N / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = K / kBK;
+    const int group = blockIdx.x / CTA_GROUP;
+    const int num_groups = gridDim.x / CTA_GROUP;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint32_t full_leader = (CTA_GROUP == 2) ? mapa_cluster(full_bar, 0) : full_bar;
+            const uint32_t empty_peer = (CTA_GROUP == 2) ? mapa_cluster(empty_bar, 1) : 0u;
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t fills = 0;  // ring slots filled so far by this CTA
+            bool ok = true;
+            for (int tile = group; tile < num_tiles && ok; tile += num_groups) {
+                int tm, tn;
+                tile_coord(tile, tiles_m, tiles_n, bs_w, tm, tn);
+                const int row_a = tm * BM + static_cast<int>(cta_rank) * kCtaM;
+                const int row_b = tn * BN + static_cast<int>(cta_rank) * T::kBRows;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    ok = mbar_wait(guard, empty_bar + 8 * s, ph ^ 1u, 0x100u + s);
+                    if (!ok) break;
+                    if constexpr (CTA_GROUP == 2) {
+                        // The slot was released by tcgen05.commit on the leader only; pass
+                        // the release on to the peer's copy of the barrier.  The first
+                        // STAGES fills find the ring empty and need no release.
+                        if (is_leader && fills >= static_cast<uint32_t>(STAGES)) {
+                            mbar_arrive_remote(empty_peer + 8 * s);
+                        }
+                    }
+                    if (is_leader) {
+                        mbar_arrive_expect_tx(full_bar + 8 * s, T::kStageBytes * CTA_GROUP);
+                    }
+                    if constexpr (CTA_GROUP == 2) {
+                        tma_load_2d_pair(ring_a + s * kAStageBytes, &tmap_a, full_leader + 8 * s,
+                                         kb * kBK, row_a);
+                        tma_load_2d_pair(ring_b + s * T::kBStageBytes, &tmap_b, full_leader + 8 * s,
+                                         kb * kBK, row_b);
+                    } else {
+                        tma_load_2d(ring_a + s * kAStageBytes, &tmap_a, full_bar + 8 * s, kb * kBK,
+                                    row_a);
+                        tma_load_2d(ring_b + s * T::kBStageBytes, &tmap_b, full_bar + 8 * s, kb * kBK,
+                                    row_b);
+                    }
+                    ++fills;
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------------- MMA issuer
+        if (lane == 0 && is_leader) {
+            constexpr uint32_t idesc = make_idesc_f16(BM, BN, /*bf16*/ 1, 0, 0);
+            int s = 0;
+            uint32_t ph = 0;
+            uint32_t local_tile = 0;
+            bool ok = true;
+            for (int tile = group; tile < num_tiles && ok; tile += num_groups, ++local_tile) {
+                const uint32_t buf = local_tile % ACC_BUFS;
+                const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
+                ok = mbar_wait(guard, accempty_bar + 8 * buf, acc_ph ^ 1u, 0x200u + buf);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    ok = mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + s * kAStageBytes);
+                    const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + s * T::kBStageBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k) {
+                        // 16 elements of K = 32 bytes inside the swizzled row = +2 in the
+                        // descriptor's 16-byte address units.
+                        mma_ss<CTA_GROUP>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                          (kb | k) != 0 ? 1u : 0u);
+                    }
+                    mma_commit<CTA_GROUP>(empty_bar + 8 * s);
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
+                }
+                if (ok) mma_commit<CTA_GROUP>(accfull_bar + 8 * buf);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------------- epilogue
+        const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
+        const uint32_t my_epi = epi_base + (warp - 2) * 2 * kEpiBoxBytes;
+        const uint32_t accfull_peer = (CTA_GROUP == 2) ? mapa_cluster(accfull_bar, 1) : 0u;
+        const uint32_t accempty_leader = (CTA_GROUP == 2) ? mapa_cluster(accempty_bar, 0) : accempty_bar;
+        uint32_t local_tile = 0;
+        uint32_t stores = 0;
+        bool ok = true;
+        for (int tile = group; tile < num_tiles && ok; tile += num_groups, ++local_tile) {
+            int tm, tn;
+            tile_coord(tile, tiles_m, tiles_n, bs_w, tm, tn);
+            const uint32_t buf = local_tile % ACC_BUFS;
+            const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
+            ok = mbar_wait(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if constexpr (CTA_GROUP == 2) {
+                if (is_leader && warp == 2 && lane == 0) mbar_arrive_remote(accfull_peer + 8 * buf);
+            }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+            const int out_row = tm * BM + static_cast<int>(cta_rank) * kCtaM + q * 32;
+#pragma unroll 1
+            for (int c = 0; c < BN / 64; ++c) {
+                uint32_t acc0[32], acc1[32];
+                tmem_ld_32x32b_x32(t_row + c * 64, acc0);
+                tmem_ld_32x32b_x32(t_row + c * 64 + 32, acc1);
+                tmem_wait_ld();
+                if (c == BN / 64 - 1) {
+                    // Accumulator fully read: hand the buffer back to the MMA issuer.
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if constexpr (CTA_GROUP == 2) {
+                            mbar_arrive_remote(accempty_leader + 8 * buf);
+                        } else {
+                            mbar_arrive(accempty_bar + 8 * buf);
+                        }
+                    }
+                }
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(acc0[2 * i]),
+                                                              __uint_as_float(acc0[2 * i + 1]));
+                    __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(acc1[2 * i]),
+                                                              __uint_as_float(acc1[2 * i + 1]));
+                    packed[i] = *reinterpret_cast<uint32_t*>(&v0);
+                    packed[16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                }
+                const uint32_t box = my_epi + (stores & 1u) * kEpiBoxBytes;
+                // The store issued two steps ago read this box; wait until it has.
+                if (lane == 0) tma_store_wait_read<1>();
+                __syncwarp();
+                const uint32_t row_addr = box + lane * 128;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    st_shared_v4(row_addr + ((j ^ (lane & 7)) << 4), packed[4 * j], packed[4 * j + 1],
+                                 packed[4 * j + 2], packed[4 * j + 3]);
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&tmap_c, box, tn * BN + c * 64, out_row);
+                    tma_store_commit();
+                }
+                ++stores;
+            }
+        }
+        if (lane == 0) tma_store_wait_all<0>();
+    }
+
+    // ------------------------------------------------------------------------- teardown
+    if (*abort_ptr != 0) {
+        // A wait gave up: let copies and MMAs already in flight retire before the shared
+        // and tensor memory they target is released.
+        for (int i = 0; i < 64; ++i) __nanosleep(100000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if constexpr (CTA_GROUP == 2) {
+        cluster_arrive();
+        cluster_wait();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc<CTA_GROUP>(tmem_base, T::kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------- host launcher
+using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
+                         int64_t, const void*, int64_t, void*, int64_t, cudaStream_t);
+
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N, int K,
+                const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
+                cudaStream_t stream) {
+    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
+    auto kernel = gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC_BUFS>;
+
+    CUtensorMap tmap_a, tmap_b, tmap_c;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+        const uint32_t box[2] = {kBK, kCtaM};
+        if (int rc = encode_tmap_2byte(&tmap_a, A, 2, dims, strides, box, true)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+        const uint32_t box[2] = {kBK, static_cast<uint32_t>(T::kBRows)};
+        if (int rc = encode_tmap_2byte(&tmap_b, B, 2, dims, strides, box, true)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldc) * 2};
+        const uint32_t box[2] = {64, kEpiBoxRows};
+        if (int rc = encode_tmap_2byte(&tmap_c, C, 2, dims, strides, box, true)) return rc;
+    }
+
+    // Set once per (kernel, device); the reference sets it on every call
+    // (gemm/gemm_cute.hpp:339-341).
+    static bool attr_done[64] = {};
+    if (!attr_done[dev->device]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+        if (e != cudaSuccess) return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", cfg.name,
+                                          T::kSmemBytes, cudaGetErrorString(e));
+        attr_done[dev->device] = true;
+    }
+
+    const int num_tiles = (M / (kCtaM * CTA_GROUP)) * (N / BN);
+    int groups = dev->sm_count / CTA_GROUP;
+    if (groups > num_tiles) groups = num_tiles;
+
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(groups * CTA_GROUP), 1, 1);
+    lc.blockDim = dim3(kThreads, 1, 1);
+    lc.dynamicSmemBytes = T::kSmemBytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = CTA_GROUP;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, M, N, K, cfg.bs_w, dev->status);
+    if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
+    return B200_OK;
+}
+
+struct Entry {
+    b200_gemm_config cfg;
+    LaunchFn launch;
+};
+
+#define B200_GEMM_CONFIG(NAME, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)                                  \
+    Entry{b200_gemm_config{NAME, kCtaM * CTA_GROUP, BN, kBK, STAGES, CTA_GROUP, ACC_BUFS, BS_W,        \
+                           GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kSmemBytes,                    \
+                           GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kTmemCols},                    \
+          &launch_gemm<BN, STAGES, CTA_GROUP, ACC_BUFS>},
+
+const Entry kEntries[] = {
+#include "generated/gemm_configs.inc"
+};
+#undef B200_GEMM_CONFIG
+
+constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
+int b200_gemm_num_configs(void) { return b200::kNumEntries; }
+
+const b200_gemm_config* b200_gemm_get_config(int idx) {
+    if (idx < 0 || idx >= b200::kNumEntries) return nullptr;
+    return &b200::kEntries[idx].cfg;
+}
+
+int b200_gemm_find_config(const char* name) {
+    if (name == nullptr) return -1;
+    for (int i = 0; i < b200::kNumEntries; ++i) {
+        if (std::strcmp(name, b200::kEntries[i].cfg.name) == 0) return i;
+    }
+    return -1;
+}
+
+int b200_gemm_default_config(int M, int N, int K) {
+    // Prefer the config with the largest tile area whose tile count still covers every SM
+    // pair at least once; fall back to the legal config with the most tiles.
+    int best = -1;
+    long best_score = -1;
+    for (int i = 0; i < b200::kNumEntries; ++i) {
+        const b200_gemm_config& c = b200::kEntries[i].cfg;
+        if (M <= 0 || N <= 0 || K <= 0 || M % c.bm || N % c.bn || K % c.bk) continue;
+        const long tiles = static_cast<long>(M / c.bm) * (N / c.bn);
+        const long ctas = tiles * c.cta_group;
+        const long area = static_cast<long>(c.bm) * c.bn;
+        // Enough tiles to occupy 148 SMs: score by tile area (then stages); otherwise by
+        // how many SMs get work.
+        const long score = (ctas >= 148) ? (1000000L + area * 8 + c.stages + c.acc_bufs)
+                                         : (ctas * 1000L + area / 1024);
+        if (score > best_score) {
+            best_score = score;
+            best = i;
+        }
+    }
+    return best;
+}
+
+int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                      int64_t ldb, void* C, int64_t ldc, void* stream) {
+    using namespace b200;
+    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
+    const Entry& e = kEntries[config];
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
+    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
+    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
+        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
+                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
+    }
+    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
+        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
+                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
+    }
+    const DeviceInfo* dev = current_device();
+    if (dev == nullptr) return B200_ENODEVICE;
+    if (e.cfg.smem_bytes > dev->max_smem_optin) {
+        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
+                    dev->max_smem_optin);
+    }
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C, ldc, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

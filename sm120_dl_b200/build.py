@@ -107,7 +107,7 @@ def build_test_gemm_cute(force=False, verbose=False):
         tmp = out + ".tmp"
         _run([NVCC] + NVCC_FLAGS + ["-x", "cu", src, os.path.join(GEMM_DIR, "gemm_config_registry.cpp"),
               "-I", os.path.join(ROOT, "include"), "-I", GEMM_DIR, "-o", tmp, "-L", HERE, "-lb200dl",
-              "-lcublas", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."], verbose)
+              "-lcublas", "-Xcompiler", "-fopenmp", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/.."], verbose)
         os.replace(tmp, out)
     return out
 

@@ -36,6 +36,14 @@ constexpr int kQTiles = 2;
 constexpr int kFaThreads = 384;
 constexpr int kBoxBytes = 128 * 128;      // one TMA box: 128 rows x 64 fp16 (128 bytes)
 constexpr float kRescaleLog2 = 8.0f;      // rescale O only when the max grew by > 2^8
+// Register budget after the role split.  setmaxnreg.inc blocks until the CTA's own pool
+// (registers per thread at launch x threads) can supply the increase, so the two budgets
+// must fit in what the CTA was launched with or the kernel never gets past the split.
+constexpr int kRegsAtLaunch = 168;        // what ptxas assigns under __launch_bounds__(384, 1)
+constexpr int kRegsLoadMma = 56;          // warps 0-3
+constexpr int kRegsSoftmax = 224;         // warps 4-11
+static_assert(kRegsLoadMma * 128 + kRegsSoftmax * 256 <= kRegsAtLaunch * kFaThreads,
+              "setmaxnreg budgets exceed the registers the CTA is launched with");
 
 template <int D, int STAGES>
 struct FaTraits {
@@ -135,7 +143,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t tmem_base = *tmem_slot_ptr;
 
     if (warp < 4) {
-        setmaxnreg_dec<64>();
+        setmaxnreg_dec<kRegsLoadMma>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- TMA producer
             uint32_t q_bytes = 0;
@@ -256,7 +264,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             }
         }
     } else {
-        setmaxnreg_inc<224>();
+        setmaxnreg_inc<kRegsSoftmax>();
         // ------------------------------------------------------------- softmax warpgroups
         const int i = (warp - 4) >> 2;                 // query tile of this warpgroup
         const int quad = warp & 3;                     // tensor-memory lane quadrant

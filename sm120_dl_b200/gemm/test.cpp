@@ -1,0 +1,667 @@
+// test_gemm_cute: verify / benchmark harness over the GEMM config registry.
+//
+// Command line, exit codes and output line formats follow the reference harness
+// (gemm/test.cpp of HugeOrca/sm120-dl; modes at :1242-1303, line formats at :205-230,
+// :449-466, :577-582, :733-786) so scripts written against it keep working:
+//
+//   test_gemm_cute --verify                    every config on the 12 built-in shapes vs cuBLAS
+//   test_gemm_cute --benchmark                 rank every config per built-in shape, write BEST.txt
+//   test_gemm_cute --benchmark M N K           rank every config on one shape
+//   test_gemm_cute M N K                       verify then benchmark one shape
+//   test_gemm_cute --func <cfg> [--verify|--benchmark]      one config on 4096^3
+//   test_gemm_cute --profile <cfg> M N K [warmup]           one launch inside cudaProfilerStart/Stop
+//   test_gemm_cute --verify-host M N K         (addition) every config vs an fp64-accumulated
+//                                              host GEMM, reports the bounded relative error
+//
+// <cfg> may carry a "gemm_tn_" prefix and may end in '*' (a prefix pattern that must match
+// exactly one config), as in the reference (:467-517).
+#include <algorithm>
+#include <cerrno>
+#include <climits>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <string>
+#include <string_view>
+#include <vector>
+
+#include <cublas_v2.h>
+#include <cuda_profiler_api.h>
+#include <unistd.h>
+
+#include "gemm_config_registry.hpp"
+
+namespace {
+
+constexpr int kWarmupIterations = 5;      // reference protocol: 5 warm-up + 25 timed launches
+constexpr int kBenchmarkIterations = 25;
+constexpr float kAbsTolerance = 1.0e-2f;  // |got-ref| <= 1e-2 + 5e-2*|ref|
+constexpr float kRelTolerance = 5.0e-2f;
+
+struct GemmShape {
+    int M, N, K;
+};
+
+// The reference's built-in shape list (gemm/test.cpp:38-61).
+constexpr GemmShape kTestShapes[] = {
+    {128, 4096, 14336},  {128, 28672, 4096},  {512, 512, 14336},    {1024, 1024, 1024},
+    {1024, 1024, 14336}, {2048, 2048, 2048},  {4096, 4096, 4096},   {4096, 4096, 14336},
+    {4096, 28672, 4096}, {8192, 8192, 8192},  {16384, 16384, 16384}, {40960, 40960, 4096},
+};
+
+bool cuda_ok(cudaError_t status, const char* what) {
+    if (status == cudaSuccess) return true;
+    std::fprintf(stderr, "CUDA error at %s: %s\n", what, cudaGetErrorString(status));
+    return false;
+}
+bool cublas_ok(cublasStatus_t status, const char* what) {
+    if (status == CUBLAS_STATUS_SUCCESS) return true;
+    std::fprintf(stderr, "cuBLAS error at %s: status %d\n", what, static_cast<int>(status));
+    return false;
+}
+
+// Device allocation that frees itself.
+struct DeviceBuffer {
+    bf16* ptr = nullptr;
+    size_t count = 0;
+    explicit DeviceBuffer(size_t n) : count(n) {
+        if (!cuda_ok(cudaMalloc(reinterpret_cast<void**>(&ptr), n * sizeof(bf16)), "cudaMalloc")) ptr = nullptr;
+    }
+    ~DeviceBuffer() {
+        if (ptr) cudaFree(ptr);
+    }
+    DeviceBuffer(const DeviceBuffer&) = delete;
+    DeviceBuffer& operator=(const DeviceBuffer&) = delete;
+    bool upload(const std::vector<bf16>& host) {
+        return ptr && cuda_ok(cudaMemcpy(ptr, host.data(), host.size() * sizeof(bf16), cudaMemcpyHostToDevice), "H2D");
+    }
+    bool download(std::vector<bf16>& host) const {
+        host.resize(count);
+        return ptr && cuda_ok(cudaMemcpy(host.data(), ptr, count * sizeof(bf16), cudaMemcpyDeviceToHost), "D2H");
+    }
+};
+
+// One generator shared by every fill, seeded like the reference (gemm/test.cpp:110-117):
+// A, B and C of successive problems consume a single stream in order.
+void fill_random(std::vector<bf16>& tensor, float lo, float hi) {
+    static std::mt19937 rng(20260509);
+    std::uniform_real_distribution<float> dist(lo, hi);
+    for (auto& value : tensor) value = __float2bfloat16(dist(rng));
+}
+
+// Host and device copies of one problem; C is pre-filled with random data so that a
+// kernel that skips part of the output fails verification (gemm/test.cpp:384-386, :596).
+struct GemmProblem {
+    int M, N, K;
+    std::vector<bf16> host_A, host_B, host_C;
+    DeviceBuffer dev_A, dev_B, dev_C;
+    GemmProblem(int m, int n, int k)
+        : M(m), N(n), K(k),
+          host_A(static_cast<size_t>(m) * k), host_B(static_cast<size_t>(n) * k), host_C(static_cast<size_t>(m) * n),
+          dev_A(host_A.size()), dev_B(host_B.size()), dev_C(host_C.size()) {
+        fill_random(host_A, -0.1f, 0.1f);
+        fill_random(host_B, -0.1f, 0.1f);
+        fill_random(host_C, -0.1f, 0.1f);
+        ok = dev_A.upload(host_A) && dev_B.upload(host_B) && dev_C.upload(host_C);
+    }
+    bool ok = false;
+};
+
+// Row-major C[M,N] = A[M,K] * B[N,K]^T through column-major cuBLAS: C^T = B * A^T
+// (same call as gemm/test.cpp:131-163).
+bool launch_cublas(cublasHandle_t handle, int M, int N, int K, const bf16* A, const bf16* B, bf16* C) {
+    const float alpha = 1.0f, beta = 0.0f;
+    return cublas_ok(cublasGemmEx(handle, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, B, CUDA_R_16BF, K, A,
+                                  CUDA_R_16BF, K, &beta, C, CUDA_R_16BF, N, CUBLAS_COMPUTE_32F,
+                                  CUBLAS_GEMM_DEFAULT_TENSOR_OP),
+                     "cublasGemmEx");
+}
+
+bool cublas_reference(cublasHandle_t handle, const GemmProblem& p, std::vector<bf16>& out) {
+    DeviceBuffer ref(static_cast<size_t>(p.M) * p.N);
+    if (!ref.ptr) return false;
+    if (!launch_cublas(handle, p.M, p.N, p.K, p.dev_A.ptr, p.dev_B.ptr, ref.ptr)) return false;
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return false;
+    return ref.download(out);
+}
+
+// Element-wise check with the reference's mixed tolerance and report lines.
+bool verify_result(const std::vector<bf16>& actual, const std::vector<bf16>& reference, int cols, bool print_detail) {
+    if (actual.size() != reference.size()) {
+        std::fprintf(stderr, "size mismatch: actual=%zu reference=%zu\n", actual.size(), reference.size());
+        return false;
+    }
+    size_t mismatches = 0, first_mismatch = actual.size(), max_idx = 0;
+    float max_abs = 0.f, max_rel = 0.f;
+    for (size_t i = 0; i < actual.size(); ++i) {
+        const float got = __bfloat162float(actual[i]);
+        const float ref = __bfloat162float(reference[i]);
+        const float diff = std::fabs(got - ref);
+        if (diff > max_abs || std::isnan(diff)) {
+            max_abs = diff;
+            max_rel = diff / std::max(std::fabs(ref), 1.0e-20f);
+            max_idx = i;
+        }
+        if (!(diff <= kAbsTolerance + kRelTolerance * std::fabs(ref))) {
+            if (first_mismatch == actual.size()) first_mismatch = i;
+            ++mismatches;
+        }
+    }
+    if (print_detail) {
+        std::printf("verify detail: max_abs=%g max_rel=%g max_idx=%zu mismatches=%zu/%zu\n", max_abs, max_rel, max_idx,
+                    mismatches, actual.size());
+    }
+    if (mismatches != 0) {
+        if (print_detail) {
+            std::fprintf(stderr, "first mismatch at linear index=%zu row=%zu col=%zu got=%g ref=%g\n", first_mismatch,
+                         first_mismatch / static_cast<size_t>(cols), first_mismatch % static_cast<size_t>(cols),
+                         __bfloat162float(actual[first_mismatch]), __bfloat162float(reference[first_mismatch]));
+        }
+        return false;
+    }
+    return true;
+}
+
+double gemm_tflops(int M, int N, int K, float ms) {
+    if (ms <= 0.f) return 0.0;
+    return 2.0 * M * N * K / (static_cast<double>(ms) * 1.0e-3) / 1.0e12;
+}
+double percent_of(double ours, double cublas) { return cublas > 0.0 ? ours / cublas * 100.0 : 0.0; }
+
+bool config_supports_problem(const GemmConfig& c, int M, int N, int K) {
+    return M % c.bm == 0 && N % c.bn == 0 && K % c.bk == 0;
+}
+
+void print_shape_braced(const GemmShape& s) { std::printf("{%d, %d, %d}", s.M, s.N, s.K); }
+
+void print_config_skipped(const char* mode, const GemmConfig& c, int M, int N, int K) {
+    std::printf("%s skipped: %s M=%d N=%d K=%d requires M%%BM==0 N%%BN==0 K%%BK==0 (BM=%d BN=%d BK=%d)\n", mode,
+                c.name, M, N, K, c.bm, c.bn, c.bk);
+}
+
+// ------------------------------------------------------------------------ config lookup
+std::string_view strip_prefix(std::string_view name) {
+    constexpr std::string_view prefix = "gemm_tn_";
+    if (name.substr(0, prefix.size()) == prefix) name.remove_prefix(prefix.size());
+    return name;
+}
+
+void print_available_configs() {
+    std::fprintf(stderr, "available configs:\n");
+    for (size_t i = 0; i < kGemmConfigCount; ++i) std::fprintf(stderr, "  gemm_tn_%s\n", kGemmConfigs[i].name);
+}
+
+// Exact name, or a pattern ending in '*' that must match exactly one config by prefix.
+const GemmConfig* find_config(std::string_view query) {
+    const std::string_view wanted = strip_prefix(query);
+    const bool pattern = !wanted.empty() && wanted.back() == '*';
+    const std::string_view stem = pattern ? wanted.substr(0, wanted.size() - 1) : wanted;
+    const GemmConfig* found = nullptr;
+    size_t matches = 0;
+    for (size_t i = 0; i < kGemmConfigCount; ++i) {
+        const std::string_view name = kGemmConfigs[i].name;
+        const bool hit = pattern ? name.substr(0, stem.size()) == stem : name == stem;
+        if (hit) {
+            found = &kGemmConfigs[i];
+            ++matches;
+        }
+    }
+    if (matches == 1) return found;
+    if (matches > 1) {
+        std::fprintf(stderr, "ambiguous config pattern: %.*s (%zu matches)\n", static_cast<int>(query.size()),
+                     query.data(), matches);
+    } else {
+        std::fprintf(stderr, "unknown config: %.*s\n", static_cast<int>(query.size()), query.data());
+    }
+    return nullptr;
+}
+
+// ------------------------------------------------------------------------------- verify
+bool run_and_check(const GemmConfig& config, const GemmProblem& p, const std::vector<bf16>& reference,
+                   bool print_detail) {
+    // Restore the random pre-fill so every config has to overwrite all of C.
+    if (!cuda_ok(cudaMemcpy(p.dev_C.ptr, p.host_C.data(), p.host_C.size() * sizeof(bf16), cudaMemcpyHostToDevice),
+                 "restore C"))
+        return false;
+    config.run(p.M, p.N, p.K, p.dev_A.ptr, p.dev_B.ptr, p.dev_C.ptr, nullptr);
+    if (!cuda_ok(cudaGetLastError(), config.name)) return false;
+    if (!cuda_ok(cudaDeviceSynchronize(), "cudaDeviceSynchronize")) return false;
+    std::vector<bf16> got;
+    if (!p.dev_C.download(got)) return false;
+    return verify_result(got, reference, p.N, print_detail);
+}
+
+void print_verify_status(const GemmShape& s, const char* status, const GemmConfig& c) {
+    print_shape_braced(s);
+    std::printf(" verify %s: %s\n", status, c.name);
+}
+
+struct VerifySummary {
+    size_t passed = 0, failed = 0, skipped = 0, total = 0;
+    bool ok = true;
+};
+
+VerifySummary verify_all_configs_for_shape(cublasHandle_t handle, const GemmShape& shape, bool print_success,
+                                           bool print_skipped) {
+    VerifySummary sum;
+    sum.total = kGemmConfigCount;
+    GemmProblem problem(shape.M, shape.N, shape.K);
+    std::vector<bf16> reference;
+    if (!problem.ok || !cublas_reference(handle, problem, reference)) {
+        sum.ok = false;
+        sum.failed = sum.total;
+    } else {
+        for (size_t i = 0; i < kGemmConfigCount; ++i) {
+            const GemmConfig& c = kGemmConfigs[i];
+            if (!config_supports_problem(c, shape.M, shape.N, shape.K)) {
+                if (print_skipped) print_verify_status(shape, "skipped", c);
+                ++sum.skipped;
+                continue;
+            }
+            if (run_and_check(c, problem, reference, false)) {
+                ++sum.passed;
+                if (print_success) print_verify_status(shape, "success", c);
+            } else {
+                print_verify_status(shape, "failed", c);
+            }
+        }
+        sum.failed = sum.total - sum.passed - sum.skipped;
+    }
+    print_shape_braced(shape);
+    std::printf(" verify summary: passed=%zu failed=%zu skipped=%zu total=%zu\n", sum.passed, sum.failed, sum.skipped,
+                sum.total);
+    return sum;
+}
+
+int run_verify() {
+    cublasHandle_t handle = nullptr;
+    if (!cublas_ok(cublasCreate(&handle), "cublasCreate")) return EXIT_FAILURE;
+    bool ok = true;
+    for (const GemmShape& shape : kTestShapes) {
+        const VerifySummary s = verify_all_configs_for_shape(handle, shape, false, false);
+        ok = ok && s.ok && s.failed == 0;
+    }
+    cublasDestroy(handle);
+    return ok ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+// ---------------------------------------------------------------------------- benchmark
+struct BenchmarkResult {
+    bool ok = false;
+    float latency_ms = 0.f;
+    double throughput = 0.0;
+};
+
+// Warm-up launches, then back-to-back timed launches between two events on a
+// non-blocking stream; the average is reported (gemm/test.cpp:232-291).
+template <class Launch>
+BenchmarkResult time_launches(int M, int N, int K, Launch&& launch) {
+    BenchmarkResult r;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate")) return r;
+    bool ok = cuda_ok(cudaEventCreate(&start), "cudaEventCreate") && cuda_ok(cudaEventCreate(&stop), "cudaEventCreate");
+    for (int i = 0; i < kWarmupIterations && ok; ++i) ok = launch(stream);
+    ok = ok && cuda_ok(cudaStreamSynchronize(stream), "warm-up sync");
+    ok = ok && cuda_ok(cudaEventRecord(start, stream), "cudaEventRecord");
+    for (int i = 0; i < kBenchmarkIterations && ok; ++i) ok = launch(stream);
+    ok = ok && cuda_ok(cudaEventRecord(stop, stream), "cudaEventRecord");
+    ok = ok && cuda_ok(cudaEventSynchronize(stop), "cudaEventSynchronize");
+    float total_ms = 0.f;
+    ok = ok && cuda_ok(cudaEventElapsedTime(&total_ms, start, stop), "cudaEventElapsedTime");
+    if (start) cudaEventDestroy(start);
+    if (stop) cudaEventDestroy(stop);
+    cudaStreamDestroy(stream);
+    if (ok) {
+        r.ok = true;
+        r.latency_ms = total_ms / kBenchmarkIterations;
+        r.throughput = gemm_tflops(M, N, K, r.latency_ms);
+    }
+    return r;
+}
+
+BenchmarkResult benchmark_config(const GemmConfig& c, const GemmProblem& p) {
+    return time_launches(p.M, p.N, p.K, [&](cudaStream_t s) {
+        c.run(p.M, p.N, p.K, p.dev_A.ptr, p.dev_B.ptr, p.dev_C.ptr, s);
+        return cuda_ok(cudaGetLastError(), c.name);
+    });
+}
+
+BenchmarkResult benchmark_cublas(const GemmProblem& p) {
+    cublasHandle_t handle = nullptr;
+    if (!cublas_ok(cublasCreate(&handle), "cublasCreate")) return {};
+    DeviceBuffer out(static_cast<size_t>(p.M) * p.N);
+    BenchmarkResult r;
+    if (out.ptr) {
+        r = time_launches(p.M, p.N, p.K, [&](cudaStream_t s) {
+            return cublas_ok(cublasSetStream(handle, s), "cublasSetStream") &&
+                   launch_cublas(handle, p.M, p.N, p.K, p.dev_A.ptr, p.dev_B.ptr, out.ptr);
+        });
+    }
+    cublasDestroy(handle);
+    return r;
+}
+
+void print_benchmark_line(size_t rank, const GemmConfig& c, const BenchmarkResult& r, const BenchmarkResult& cublas) {
+    std::printf("%4zu. %s %.4f ms %.3f TFLOP/s cublas %.4f ms %.3f TFLOP/s gemm_tn/cublas=%.2f%%\n", rank, c.name,
+                r.latency_ms, r.throughput, cublas.latency_ms, cublas.throughput,
+                percent_of(r.throughput, cublas.throughput));
+}
+void print_benchmark_result(const GemmConfig& c, const BenchmarkResult& r, const BenchmarkResult& cublas) {
+    std::printf("%s %.4f ms %.3f TFLOP/s cublas %.4f ms %.3f TFLOP/s gemm_tn/cublas=%.2f%%\n", c.name, r.latency_ms,
+                r.throughput, cublas.latency_ms, cublas.throughput, percent_of(r.throughput, cublas.throughput));
+}
+// "BEST:" lines are parsed by profiling scripts (gemm/test_compute_rate.py:43 of the
+// reference); the format is kept byte for byte (gemm/test.cpp:765-786).
+std::string format_best_line(const GemmShape& s, const GemmConfig& c, const BenchmarkResult& r,
+                             const BenchmarkResult& cublas) {
+    char line[1024];
+    std::snprintf(line, sizeof(line),
+                  "BEST: %d,%d,%d %s   %.4f ms %.3f TFLOP/s cublas %.4f ms %.3f TFLOP/s gemm_tn/cublas=%.2f%%\n", s.M,
+                  s.N, s.K, c.name, r.latency_ms, r.throughput, cublas.latency_ms, cublas.throughput,
+                  percent_of(r.throughput, cublas.throughput));
+    return line;
+}
+
+struct ShapeBenchmark {
+    bool ok = true;
+    size_t failed = 0;
+    GemmShape shape{};
+    const GemmConfig* best = nullptr;
+    BenchmarkResult best_result, cublas;
+};
+
+ShapeBenchmark benchmark_all_configs_for_shape(const GemmShape& shape) {
+    ShapeBenchmark out;
+    out.shape = shape;
+    GemmProblem problem(shape.M, shape.N, shape.K);
+    if (!problem.ok) {
+        out.ok = false;
+        return out;
+    }
+    out.cublas = benchmark_cublas(problem);
+    if (!out.cublas.ok) out.ok = false;
+
+    struct Row {
+        const GemmConfig* config;
+        BenchmarkResult result;
+    };
+    std::vector<Row> rows;
+    for (size_t i = 0; i < kGemmConfigCount; ++i) {
+        const GemmConfig& c = kGemmConfigs[i];
+        if (!config_supports_problem(c, shape.M, shape.N, shape.K)) continue;
+        Row row{&c, benchmark_config(c, problem)};
+        if (!row.result.ok) ++out.failed;
+        rows.push_back(row);
+    }
+    std::stable_sort(rows.begin(), rows.end(), [](const Row& a, const Row& b) {
+        if (a.result.ok != b.result.ok) return a.result.ok;
+        return a.result.throughput > b.result.throughput;
+    });
+    print_shape_braced(shape);
+    std::printf(" benchmark\n");
+    size_t rank = 1;
+    for (const Row& row : rows) {
+        if (row.result.ok) {
+            print_benchmark_line(rank, *row.config, row.result, out.cublas);
+        } else {
+            std::printf("%4zu. %s FAILED\n", rank, row.config->name);
+        }
+        ++rank;
+    }
+    if (!rows.empty() && rows.front().result.ok) {
+        out.best = rows.front().config;
+        out.best_result = rows.front().result;
+    }
+    return out;
+}
+
+std::string executable_dir() {
+    char buf[4096];
+    const ssize_t n = readlink("/proc/self/exe", buf, sizeof(buf) - 1);
+    if (n <= 0) return ".";
+    buf[n] = '\0';
+    std::string path(buf);
+    const size_t slash = path.find_last_of('/');
+    if (slash == std::string::npos) return ".";
+    return slash == 0 ? "/" : path.substr(0, slash);
+}
+
+// BEST.txt lives next to the executable (gemm/test.cpp:546-566, :952-980).
+bool write_best_file(const std::vector<std::string>& lines) {
+    const std::string path = executable_dir() + "/BEST.txt";
+    FILE* f = std::fopen(path.c_str(), "w");
+    if (!f) {
+        std::fprintf(stderr, "failed to open %s: %s\n", path.c_str(), std::strerror(errno));
+        return false;
+    }
+    bool ok = true;
+    for (const std::string& line : lines) {
+        if (std::fputs(line.c_str(), f) == EOF) {
+            std::fprintf(stderr, "failed to write %s: %s\n", path.c_str(), std::strerror(errno));
+            ok = false;
+            break;
+        }
+    }
+    if (std::fclose(f) != 0) {
+        std::fprintf(stderr, "failed to close %s: %s\n", path.c_str(), std::strerror(errno));
+        ok = false;
+    }
+    return ok;
+}
+
+int run_benchmark() {
+    bool ok = true;
+    std::vector<std::string> best_lines;
+    for (const GemmShape& shape : kTestShapes) {
+        const ShapeBenchmark r = benchmark_all_configs_for_shape(shape);
+        ok = ok && r.ok && r.failed == 0 && r.best != nullptr;
+        if (r.best) {
+            const std::string line = format_best_line(shape, *r.best, r.best_result, r.cublas);
+            std::fputs(line.c_str(), stdout);
+            best_lines.push_back(line);
+        }
+    }
+    ok = write_best_file(best_lines) && ok;
+    return ok ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+int run_shape_benchmark(const GemmShape& shape) {
+    const ShapeBenchmark r = benchmark_all_configs_for_shape(shape);
+    if (r.best) std::fputs(format_best_line(shape, *r.best, r.best_result, r.cublas).c_str(), stdout);
+    return r.ok && r.failed == 0 && r.best ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+int run_shape_test(const GemmShape& shape) {
+    cublasHandle_t handle = nullptr;
+    if (!cublas_ok(cublasCreate(&handle), "cublasCreate")) return EXIT_FAILURE;
+    const VerifySummary v = verify_all_configs_for_shape(handle, shape, true, true);
+    cublasDestroy(handle);
+    const ShapeBenchmark r = benchmark_all_configs_for_shape(shape);
+    if (r.best) std::fputs(format_best_line(shape, *r.best, r.best_result, r.cublas).c_str(), stdout);
+    return v.ok && v.failed == 0 && r.ok && r.failed == 0 && r.best ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+// ------------------------------------------------------------------- --func / --profile
+enum class FuncMode { VerifyAndBenchmark, VerifyOnly, BenchmarkOnly };
+
+const char* func_mode_name(FuncMode m) {
+    switch (m) {
+        case FuncMode::VerifyOnly: return "verify";
+        case FuncMode::BenchmarkOnly: return "benchmark";
+        default: return "verify+benchmark";
+    }
+}
+
+int run_func(std::string_view query, FuncMode mode) {
+    constexpr GemmShape shape{4096, 4096, 4096};
+    const GemmConfig* config = find_config(query);
+    if (!config) {
+        print_available_configs();
+        return EXIT_FAILURE;
+    }
+    if (!config_supports_problem(*config, shape.M, shape.N, shape.K)) {
+        print_config_skipped("func", *config, shape.M, shape.N, shape.K);
+        return EXIT_FAILURE;
+    }
+    std::printf("func config=%s mode=%s M=%d N=%d K=%d warmup=%d iterations=%d\n", config->name, func_mode_name(mode),
+                shape.M, shape.N, shape.K, kWarmupIterations, kBenchmarkIterations);
+    GemmProblem problem(shape.M, shape.N, shape.K);
+    if (!problem.ok) return EXIT_FAILURE;
+    bool verify_ok = true, bench_ok = true;
+    if (mode != FuncMode::BenchmarkOnly) {
+        cublasHandle_t handle = nullptr;
+        std::vector<bf16> reference;
+        verify_ok = cublas_ok(cublasCreate(&handle), "cublasCreate") && cublas_reference(handle, problem, reference) &&
+                    run_and_check(*config, problem, reference, true);
+        if (handle) cublasDestroy(handle);
+        std::printf("verify %s: %s\n", verify_ok ? "success" : "failed", config->name);
+    }
+    if (mode != FuncMode::VerifyOnly) {
+        const BenchmarkResult cublas = benchmark_cublas(problem);
+        const BenchmarkResult r = benchmark_config(*config, problem);
+        bench_ok = r.ok && cublas.ok;
+        if (bench_ok) print_benchmark_result(*config, r, cublas);
+    }
+    return verify_ok && bench_ok ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+// Warm-up launches, then exactly one launch between cudaProfilerStart/Stop so a profiler
+// started with "--profile-from-start off" captures a single kernel (gemm/test.cpp:1138-1194).
+int run_profile(std::string_view query, const GemmShape& shape, int warmup) {
+    const GemmConfig* config = find_config(query);
+    if (!config) {
+        print_available_configs();
+        return EXIT_FAILURE;
+    }
+    if (!config_supports_problem(*config, shape.M, shape.N, shape.K)) {
+        print_config_skipped("profile", *config, shape.M, shape.N, shape.K);
+        return EXIT_FAILURE;
+    }
+    std::printf("profile config=%s M=%d N=%d K=%d warmup=%d\n", config->name, shape.M, shape.N, shape.K, warmup);
+    GemmProblem problem(shape.M, shape.N, shape.K);
+    if (!problem.ok) return EXIT_FAILURE;
+    cudaStream_t stream = nullptr;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking), "cudaStreamCreate")) return EXIT_FAILURE;
+    auto launch = [&]() {
+        config->run(shape.M, shape.N, shape.K, problem.dev_A.ptr, problem.dev_B.ptr, problem.dev_C.ptr, stream);
+        return cuda_ok(cudaGetLastError(), config->name);
+    };
+    bool ok = true;
+    for (int i = 0; i < warmup && ok; ++i) ok = launch();
+    ok = ok && cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (ok) {
+        cudaProfilerStart();
+        ok = launch();
+        ok = ok && cuda_ok(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+        cudaProfilerStop();
+    }
+    cudaStreamDestroy(stream);
+    return ok ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+// ------------------------------------------------------------------------ --verify-host
+// Every legal config against a host GEMM that widens bf16 to double and accumulates in
+// double; reports max |got-ref| / max(|ref|, rms(ref)), the relative error that stays
+// bounded where ref is close to zero.  Pass bound: 1e-2.
+int run_verify_host(const GemmShape& shape) {
+    GemmProblem p(shape.M, shape.N, shape.K);
+    if (!p.ok) return EXIT_FAILURE;
+    const size_t mn = static_cast<size_t>(shape.M) * shape.N;
+    std::vector<double> ref(mn);
+    std::vector<double> a(p.host_A.size()), b(p.host_B.size());
+    for (size_t i = 0; i < a.size(); ++i) a[i] = __bfloat162float(p.host_A[i]);
+    for (size_t i = 0; i < b.size(); ++i) b[i] = __bfloat162float(p.host_B[i]);
+    double sumsq = 0.0;
+#pragma omp parallel for reduction(+ : sumsq) schedule(static)
+    for (long m = 0; m < shape.M; ++m) {
+        for (int n = 0; n < shape.N; ++n) {
+            const double* ar = &a[static_cast<size_t>(m) * shape.K];
+            const double* br = &b[static_cast<size_t>(n) * shape.K];
+            double acc = 0.0;
+            for (int k = 0; k < shape.K; ++k) acc += ar[k] * br[k];
+            ref[static_cast<size_t>(m) * shape.N + n] = acc;
+            sumsq += acc * acc;
+        }
+    }
+    const double rms = std::sqrt(sumsq / static_cast<double>(mn));
+    bool all_ok = true;
+    for (size_t i = 0; i < kGemmConfigCount; ++i) {
+        const GemmConfig& c = kGemmConfigs[i];
+        if (!config_supports_problem(c, shape.M, shape.N, shape.K)) continue;
+        cudaMemcpy(p.dev_C.ptr, p.host_C.data(), mn * sizeof(bf16), cudaMemcpyHostToDevice);
+        c.run(shape.M, shape.N, shape.K, p.dev_A.ptr, p.dev_B.ptr, p.dev_C.ptr, nullptr);
+        std::vector<bf16> got;
+        if (!cuda_ok(cudaDeviceSynchronize(), c.name) || !p.dev_C.download(got)) return EXIT_FAILURE;
+        double worst = 0.0;
+        for (size_t j = 0; j < mn; ++j) {
+            const double g = __bfloat162float(got[j]);
+            const double e = std::isfinite(g) ? std::fabs(g - ref[j]) / std::max(std::fabs(ref[j]), rms) : INFINITY;
+            worst = std::max(worst, e);
+        }
+        const bool ok = worst <= 1.0e-2;
+        all_ok = all_ok && ok;
+        print_shape_braced(shape);
+        std::printf(" verify-host %s: %s max_rel=%g\n", ok ? "success" : "failed", c.name, worst);
+    }
+    return all_ok ? EXIT_SUCCESS : EXIT_FAILURE;
+}
+
+void print_usage(const char* program) {
+    std::fprintf(stderr,
+                 "usage: %s --verify|--benchmark|--benchmark m n k|m n k"
+                 "|--func <gemm_tn_config_name> [--verify|--benchmark]"
+                 "|--profile <gemm_tn_config_name> m n k [warmup]|--verify-host m n k\n",
+                 program);
+}
+
+bool parse_positive_int(const char* text, int& value) {
+    errno = 0;
+    char* end = nullptr;
+    const long parsed = std::strtol(text, &end, 10);
+    if (errno != 0 || end == text || *end != '\0' || parsed <= 0 || parsed > INT_MAX) return false;
+    value = static_cast<int>(parsed);
+    return true;
+}
+bool parse_shape(char** argv, GemmShape& s) {
+    return parse_positive_int(argv[0], s.M) && parse_positive_int(argv[1], s.N) && parse_positive_int(argv[2], s.K);
+}
+
+}  // namespace
+
+int main(int argc, char** argv) {
+    GemmShape shape{};
+    if (argc == 2 && std::strcmp(argv[1], "--verify") == 0) return run_verify();
+    if (argc == 2 && std::strcmp(argv[1], "--benchmark") == 0) return run_benchmark();
+    if (argc == 5 && std::strcmp(argv[1], "--benchmark") == 0) {
+        if (!parse_shape(argv + 2, shape)) return print_usage(argv[0]), EXIT_FAILURE;
+        return run_shape_benchmark(shape);
+    }
+    if (argc == 5 && std::strcmp(argv[1], "--verify-host") == 0) {
+        if (!parse_shape(argv + 2, shape)) return print_usage(argv[0]), EXIT_FAILURE;
+        return run_verify_host(shape);
+    }
+    if ((argc == 3 || argc == 4) && std::strcmp(argv[1], "--func") == 0) {
+        FuncMode mode = FuncMode::VerifyAndBenchmark;
+        if (argc == 4) {
+            if (std::strcmp(argv[3], "--verify") == 0) mode = FuncMode::VerifyOnly;
+            else if (std::strcmp(argv[3], "--benchmark") == 0) mode = FuncMode::BenchmarkOnly;
+            else return print_usage(argv[0]), EXIT_FAILURE;
+        }
+        return run_func(argv[2], mode);
+    }
+    if ((argc == 6 || argc == 7) && std::strcmp(argv[1], "--profile") == 0) {
+        int warmup = 3;
+        if (!parse_shape(argv + 3, shape) || (argc == 7 && !parse_positive_int(argv[6], warmup)))
+            return print_usage(argv[0]), EXIT_FAILURE;
+        return run_profile(argv[2], shape, warmup);
+    }
+    if (argc == 4) {
+        if (!parse_shape(argv + 1, shape)) return print_usage(argv[0]), EXIT_FAILURE;
+        return run_shape_test(shape);
+    }
+    print_usage(argv[0]);
+    return EXIT_FAILURE;
+}

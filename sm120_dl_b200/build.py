@@ -49,10 +49,12 @@ def generate_configs(verbose=False):
     sys.path.insert(0, GEMM_DIR)
     sys.path.insert(0, FA_DIR)
     try:
+        import contextlib
+        import io
         import gemm_configs
-        gemm_configs.main([])
-        if os.path.exists(os.path.join(FA_DIR, "flash_configs.py")):
-            import flash_configs
+        import flash_configs
+        with contextlib.redirect_stdout(io.StringIO()):
+            gemm_configs.main([])
             flash_configs.main([])
     finally:
         sys.path.remove(GEMM_DIR)
@@ -63,8 +65,7 @@ def build_lib(force=False, verbose=False, ptxas_verbose=False):
     gen_dir = os.path.join(CSRC, "generated")
     generators = [os.path.join(GEMM_DIR, "gemm_configs.py"), os.path.join(FA_DIR, "flash_configs.py")]
     incs = [os.path.join(gen_dir, "gemm_configs.inc"), os.path.join(gen_dir, "flash_configs.inc")]
-    if force or any(_newer(generators, inc) for inc in incs if "flash" not in inc or os.path.exists(generators[1])):
-        generate_configs(verbose)
+    generate_configs(verbose)  # cheap; files are rewritten only when their content changes
     units = sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".h", ".cuh"))]
     headers += [os.path.join(ROOT, "include", "b200dl.h")] + [i for i in incs if os.path.exists(i)]

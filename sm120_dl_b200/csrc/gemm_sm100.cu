@@ -416,10 +416,12 @@ int b200_gemm_default_config(int M, int N, int K) {
         const long tiles = static_cast<long>(M / c.bm) * (N / c.bn);
         const long ctas = tiles * c.cta_group;
         const long area = static_cast<long>(c.bm) * c.bn;
-        // Enough tiles to occupy 148 SMs: score by tile area (then stages); otherwise by
-        // how many SMs get work.
-        const long score = (ctas >= 148) ? (1000000L + area * 8 + c.stages + c.acc_bufs)
-                                         : (ctas * 1000L + area / 1024);
+        // Enough tiles to occupy 148 SMs: largest tile, then deepest ring, strip width 8
+        // (fastest measured on 8192^3).  Otherwise: most SMs busy, single-CTA MMA first
+        // (no pair synchronisation to pay for on a latency-bound problem), then larger tile.
+        const long score = (ctas >= 148)
+                               ? (1000000000L + area * 64 + c.stages * 4 + (c.bs_w == 8 ? 2 : 0) + c.cta_group)
+                               : (ctas * 100000L + (c.cta_group == 1 ? 50000L : 0L) + area / 64 + c.stages);
         if (score > best_score) {
             best_score = score;
             best = i;

@@ -1,0 +1,176 @@
+"""GPU parity tests of the BF16 GEMM, called through the C ABI (ctypes), checked against
+the CPU oracle on the same seeded inputs.
+
+Tolerances: the reference harness's rule |got-ref| <= 1e-2 + 5e-2*|ref| (gemm/test.cpp:29-30
+of HugeOrca/sm120-dl) AND max |got-ref| / max(|ref|, rms(ref)) <= 1e-2 against the
+fp64-accumulated host GEMM (the output is rounded to bf16: half an ulp is 2^-9 = 0.002
+relative)."""
+
+import ctypes
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+REL_BOUND = 1e-2
+
+
+@pytest.fixture(scope="module")
+def env(cuda_device, oracle):
+    import torch
+    from sm120_dl_b200 import capi
+    return torch, capi, capi.lib(), oracle, cuda_device
+
+
+def _to_dev(torch, bits, dev, dtype):
+    return torch.from_numpy(bits.view(np.int16)).to(dev).view(dtype)
+
+
+def _run(env, cfg, a, b, M, N, K, c=None, lda=None, ldb=None, ldc=None):
+    torch, capi, lib, _, dev = env
+    if c is None:
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)  # poison: every element must be written
+    rc = lib.b200_gemm_bf16_tn(cfg, M, N, K, a.data_ptr(), lda or K, b.data_ptr(), ldb or K, c.data_ptr(),
+                               ldc or N, None)
+    assert rc == 0, lib.b200_last_error().decode()
+    assert capi.device_status() == 0
+    return c
+
+
+def _check(oracle, got, ref):
+    st = oracle.compare(got, ref, 1e-2, 5e-2)
+    assert st["passed"], st
+    assert st["max_rel_bounded"] <= REL_BOUND, st
+    return st
+
+
+def test_config1_512_cubed_uniform(env):
+    """M=N=K=512, uniform[-1,1], seed 0: every config that divides the shape."""
+    torch, capi, lib, oracle, dev = env
+    a_bits, b_bits = oracle.make_gemm_inputs(512, 512, 512, 0, "uniform1")
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    ran = 0
+    for i, cfg in enumerate(capi.gemm_configs()):
+        if 512 % cfg["bm"] or 512 % cfg["bn"]:
+            continue
+        c = _run(env, i, a, b, 512, 512, 512)
+        _check(oracle, c.float().cpu().numpy(), ref)
+        ran += 1
+    assert ran >= 12
+
+
+@pytest.mark.parametrize("kblocks", [1, 2, 7, 23])
+def test_every_config_on_its_smallest_shapes(env, kblocks):
+    """One tile and 2x3 tiles per config, with K from one k-block up (ring wrap-around)."""
+    torch, capi, lib, oracle, dev = env
+    for i, cfg in enumerate(capi.gemm_configs()):
+        if cfg["bs_w"] != 8 and kblocks != 2:
+            continue  # raster width changes tile order only; cover it once
+        for tm, tn in ((1, 1), (2, 3)):
+            M, N, K = cfg["bm"] * tm, cfg["bn"] * tn, 64 * kblocks
+            a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 100 + i, "uniform01")
+            a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+            c = _run(env, i, a, b, M, N, K)
+            _check(oracle, c.float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits))
+
+
+def test_identity_b_reproduces_a_exactly(env):
+    """B = I: C must equal A bit for bit (catches a wrong swizzle or lane mapping)."""
+    torch, capi, lib, oracle, dev = env
+    K = N = 512
+    M = 768
+    a_bits, _ = oracle.make_gemm_inputs(M, 8, K, 5, "uniform1")
+    a = _to_dev(torch, a_bits, dev, torch.bfloat16)
+    eye = torch.eye(N, K, dtype=torch.bfloat16, device=dev)
+    for name in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn128_bk64_s6_cta1_acc2_bsw8",
+                 "bf16_bm256_bn64_bk64_s8_cta2_acc2_bsw8"):
+        c = _run(env, lib.b200_gemm_find_config(name.encode()), a, eye, M, N, K)
+        assert torch.equal(c.view(torch.int16), a.view(torch.int16)), name
+
+
+def test_deterministic_and_many_tiles_per_cta(env):
+    """More tiles than CTAs (persistent loop + accumulator double buffering), run twice."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = 4096, 3072, 256
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 6)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    for name in ("bf16_bm128_bn64_bk64_s8_cta1_acc2_bsw8", "bf16_bm256_bn128_bk64_s8_cta2_acc2_bsw8"):
+        idx = lib.b200_gemm_find_config(name.encode())
+        c1 = _run(env, idx, a, b, M, N, K)
+        c2 = _run(env, idx, a, b, M, N, K)
+        assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
+        _check(oracle, c1.float().cpu().numpy(), ref)
+
+
+def test_leading_dimensions_column_slab(env):
+    """An N-shard writes its slab of a full-width C and reads a row slab of B."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = 512, 1024, 384
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 8)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    full = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+    idx = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
+    for n0 in range(0, N, 256):
+        _run(env, idx, a, b[n0:n0 + 256], M, 256, K, c=full[:, n0:n0 + 256], ldc=N)
+    _check(oracle, full.float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits))
+    # padded A (lda > K): the padding must not be read
+    a_pad = torch.full((M, K + 64), float("nan"), dtype=torch.bfloat16, device=dev)
+    a_pad[:, :K] = a
+    c = _run(env, idx, a_pad, b, M, N, K, lda=K + 64)
+    _check(oracle, c.float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits))
+
+
+def test_config2_8192_cubed_rows_and_linearity(env):
+    """M=N=K=8192, N(0,1)/sqrt(K), seed 1.  The oracle checks a seeded subset of rows (each
+    output row depends on one row of A and all of B); a size-independent property covers
+    the rest: the column sums of C equal (sum of A's rows) @ B^T."""
+    torch, capi, lib, oracle, dev = env
+    n = 8192
+    a_bits, b_bits = oracle.make_gemm_inputs(n, n, n, 1)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    idx = lib.b200_gemm_default_config(n, n, n)
+    assert lib.b200_gemm_get_config(idx).contents.cta_group == 2
+    c = _run(env, idx, a, b, n, n, n)
+    rng = np.random.Generator(np.random.PCG64(1))
+    for r0 in sorted(rng.choice(n // 64, size=3, replace=False) * 64):
+        ref = oracle.gemm_f64(a_bits, b_bits, row_begin=int(r0), row_count=64)
+        _check(oracle, c[r0:r0 + 64].float().cpu().numpy(), ref)
+    col_sums = c.double().sum(dim=0).cpu().numpy()
+    a_sum = oracle.f32_from_bf16_bits(a_bits).astype(np.float64).sum(axis=0)
+    expect = oracle.f32_from_bf16_bits(b_bits).astype(np.float64) @ a_sum
+    # 8192 outputs per column, each off by at most half a bf16 ulp of a value of size ~1/sqrt(K)*...;
+    # rounding errors are unbiased, so the sum stays within a few parts in 1e3 of the column scale
+    assert np.abs(col_sums - expect).max() <= 2e-3 * np.sqrt(n) * c.float().abs().max().item()
+
+
+def test_error_paths(env):
+    torch, capi, lib, oracle, dev = env
+    a = torch.zeros(256, 64, dtype=torch.bfloat16, device=dev)
+    idx = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
+    assert lib.b200_gemm_bf16_tn(idx, 256, 128, 64, a.data_ptr(), 64, a.data_ptr(), 64, a.data_ptr(), 128, None) == -2
+    assert b"not divisible" in lib.b200_last_error()
+    # a base pointer that is not 16-byte aligned cannot be described to the TMA engine
+    assert lib.b200_gemm_bf16_tn(idx, 256, 256, 64, a.data_ptr() + 2, 64, a.data_ptr(), 64, a.data_ptr(), 256, None) == -1
+    assert b"aligned" in lib.b200_last_error()
+    assert capi.device_status() == 0
+
+
+def test_python_operator_and_streams(env):
+    torch, capi, lib, oracle, dev = env
+    from sm120_dl_b200 import ops
+    a_bits, b_bits = oracle.make_gemm_inputs(256, 512, 128, 12)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        c = ops.gemm_bf16_tn(a, b)
+    s.synchronize()
+    _check(oracle, c.float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits))
+    with pytest.raises(ValueError):
+        ops.gemm_bf16_tn(a, b[:, :64])
+    with pytest.raises(ValueError):
+        ops.gemm_bf16_tn(a.float(), b)
+    with pytest.raises(capi.B200Error):
+        ops.gemm_bf16_tn(a[:100], b)

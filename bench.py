@@ -50,8 +50,9 @@ WORKLOADS = {
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
-# under profiles/ (null until a capture of that kernel exists).
-DRAM_TRAFFIC_BYTES = {"gemm8192": None, "fa_d128": None, "fa_d64": None}
+# under profiles/ (null until a capture of that kernel exists).  fa_d128: the capture is the
+# batch-1 slice of the workload (116.1 MB); traffic grows with the batch, so x4.
+DRAM_TRAFFIC_BYTES = {"gemm8192": 1.224e9, "fa_d128": 4 * 116.1e6, "fa_d64": None}
 
 
 def flops_per_step(w):

@@ -47,7 +47,7 @@ def test_func_mode_with_prefix_and_pattern(exe):
     assert p.returncode == 0, p.stdout + p.stderr
     assert "func config=bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8 mode=verify M=4096 N=4096 K=4096 warmup=5 iterations=25" in p.stdout
     assert re.search(r"verify detail: max_abs=\S+ max_rel=\S+ max_idx=\d+ mismatches=0/16777216", p.stdout)
-    p = _run(exe, "--func", "bf16_bm128_bn192_bk64_s4*", "--benchmark")
+    p = _run(exe, "--func", "bf16_bm128_bn128_bk64_s5*", "--benchmark")
     assert p.returncode == 0 and "TFLOP/s cublas" in p.stdout
     p = _run(exe, "--func", "bf16_bm256_bn256*")
     assert p.returncode != 0 and "ambiguous config pattern" in p.stderr

@@ -64,6 +64,27 @@ int b200_gemm_default_config(int M, int N, int K);
 int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                       int64_t ldb, void* C, int64_t ldc, void* stream);
 
+/* Same computation, arguments and result as b200_gemm_bf16_tn, for callers that must not
+ * allocate device memory: code running after a framework has reserved the whole GPU for its
+ * own pool, services with a fixed memory budget that forbid allocation once they are
+ * started, and latency-critical loops where an allocator call is not acceptable.  (This
+ * entry point has no counterpart in the reference, whose launcher allocates nothing but
+ * also keeps no status.)  b200_gemm_bf16_tn allocates a 256-byte status block with
+ * cudaMalloc the first time it runs on a device; this variant instead uses a 256-byte
+ * array that is part of the library image, so it calls no cudaMalloc, cudaFree or any
+ * other allocating routine.  Every GPU that loads the library holds those 256 bytes
+ * until the process exits.
+ *   - Limit: the array serves at most 256 bytes of scratch per launch; a launch that would
+ *     need more is refused with B200_ESHAPE and a message (every current config needs 256).
+ *   - The first call on each device resolves the array's device address and reads the
+ *     device attributes; make that first call before starting any stream capture.
+ *   - All calls share the one array.  Each call clears it on `stream` before its kernel
+ *     runs, so calls that overlap on the GPU (different streams) race on it: their results
+ *     in C are still correct, but the recorded status is unreliable.  The block written by
+ *     this variant is not reported by b200_device_status. */
+int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda,
+                              const void* B, int64_t ldb, void* C, int64_t ldc, void* stream);
+
 /* ------------------------------------------------------------- attention config registry
  * Replaces `kFlashFwdConfigs[] / kFlashFwdConfigCount / kFlashFwdDefaultConfigName`
  * (flashattention/v3_mMnNkN/pybind/flash_fwd_config_registry.hpp.in:7-30). */

@@ -19,6 +19,7 @@
 // mbarrier arrive, so no multicast form of any instruction is used.
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "ptx_sm100.cuh"
 #include "runtime.h"
@@ -385,6 +386,60 @@ const Entry kEntries[] = {
 
 constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
 
+// ---------------------------------------------------------------- allocation-free variant
+// Scratch for b200_gemm_bf16_tn_noalloc: the block the kernel writes its status word into
+// when a bounded wait gives up.  It lives in the library image, so every GPU that loads
+// the library holds these 256 bytes until the process exits, and no call has to allocate.
+// The name below is only a host-side stand-in for the symbol: host code must ask the
+// runtime for the device address (cudaGetSymbolAddress) and may not pass the name itself.
+constexpr size_t kNoAllocScratchBytes = 256;   // maximum scratch the variant can serve
+constexpr size_t kStatusBlockBytes = 256;      // what one GEMM launch needs
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocDevice {
+    bool ready = false;
+    DeviceInfo info;
+};
+NoAllocDevice g_noalloc_devices[64];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: read the device facts the launcher needs
+// and resolve the device address of the scratch array.  Calls nothing that allocates.
+const DeviceInfo* noalloc_device() {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        fail(B200_ENODEVICE, "cudaGetDevice failed or device index out of range: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& slot = g_noalloc_devices[dev];
+    if (slot.ready) return &slot.info;
+    DeviceInfo info;
+    info.device = dev;
+    if ((e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess ||
+        (e = cudaDeviceGetAttribute(&info.max_smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev)) != cudaSuccess) {
+        fail(B200_ECUDA, "cudaDeviceGetAttribute failed: %s", cudaGetErrorString(e));
+        return nullptr;
+    }
+    if (info.cc_major != 10) {
+        fail(B200_ENODEVICE, "device %d has compute capability %d.x; this library contains sm_100a code only", dev,
+             info.cc_major);
+        return nullptr;
+    }
+    void* scratch = nullptr;
+    e = cudaGetSymbolAddress(&scratch, g_noalloc_scratch);
+    if (e != cudaSuccess || scratch == nullptr) {
+        fail(B200_ECUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev, cudaGetErrorString(e));
+        return nullptr;
+    }
+    info.status = static_cast<uint32_t*>(scratch);
+    slot.info = info;
+    slot.ready = true;
+    return &slot.info;
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -451,6 +506,40 @@ int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t ld
         return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
                     dev->max_smem_optin);
     }
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C, ldc, static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* C, int64_t ldc, void* stream) {
+    using namespace b200;
+    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
+    const Entry& e = kEntries[config];
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
+    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
+    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
+        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
+                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
+    }
+    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
+        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
+                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
+    }
+    // Scratch this launch needs against what the built-in array can serve.
+    const size_t scratch_needed = kStatusBlockBytes;
+    if (scratch_needed > kNoAllocScratchBytes) {
+        return fail(B200_ESHAPE, "%s on %dx%dx%d needs %zu bytes of scratch; the allocation-free entry point serves at most %zu",
+                    e.cfg.name, M, N, K, scratch_needed, kNoAllocScratchBytes);
+    }
+    const DeviceInfo* dev = noalloc_device();
+    if (dev == nullptr) return B200_ENODEVICE;
+    if (e.cfg.smem_bytes > dev->max_smem_optin) {
+        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
+                    dev->max_smem_optin);
+    }
+    // The array keeps whatever the previous call left; the status word must start at zero
+    // for this launch's record.  Ordered on the caller's stream, ahead of the kernel.
+    cudaError_t ce = cudaMemsetAsync(dev->status, 0, kStatusBlockBytes, static_cast<cudaStream_t>(stream));
+    if (ce != cudaSuccess) return fail(B200_ECUDA, "clearing the scratch block failed: %s", cudaGetErrorString(ce));
     return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C, ldc, static_cast<cudaStream_t>(stream));
 }
 

@@ -166,6 +166,7 @@ def run_reference(args):
     if rank != 0:
         return 0
     from oracle import oracle
+    oracle.use_all_cores()
     w = WORKLOADS[args.workload]
     inputs = host_inputs(args.workload)
     scale = min(1.0, 20.0 / max(args.steps, 1))   # keep the whole run within a few minutes
@@ -317,6 +318,7 @@ def run_gpu(args):
         }
         if not args.no_cpu_baseline:
             from oracle import oracle
+            oracle.use_all_cores()
             dt, fl, desc = cpu_sample(args.workload, inputs)
             line["cpu_baseline"] = {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": oracle.num_threads(),
                                     "kind": "port", "sample": desc, "seconds": dt}

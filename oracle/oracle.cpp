@@ -114,6 +114,15 @@ int oracle_num_threads(void) {
 #endif
 }
 
+// Launchers such as torchrun export OMP_NUM_THREADS=1; the CPU baseline wants every core.
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 // C (double, leading dimension ldc) = A * B^T for rows [row_begin, row_begin + row_count)
 // of A.  A, B are raw bf16 bit patterns.  C is indexed C[(m - row_begin) * ldc + n].
 void oracle_gemm_bf16_tn_f64(int M, int N, int K, const uint16_t* A, int64_t lda,

@@ -50,6 +50,8 @@ def lib():
         L = ctypes.CDLL(_LIB_PATH)
         i64p = ctypes.POINTER(ctypes.c_int64)
         L.oracle_num_threads.restype = ctypes.c_int
+        L.oracle_set_num_threads.restype = None
+        L.oracle_set_num_threads.argtypes = [ctypes.c_int]
         L.oracle_gemm_bf16_tn_f64.restype = None
         L.oracle_gemm_bf16_tn_f64.argtypes = [
             ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_int64,
@@ -69,6 +71,17 @@ def lib():
 
 def num_threads():
     return int(lib().oracle_num_threads())
+
+
+def use_all_cores():
+    """Use every core this process may run on, whatever OMP_NUM_THREADS says (torchrun
+    exports OMP_NUM_THREADS=1).  Returns the thread count now in effect."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    lib().oracle_set_num_threads(n)
+    return num_threads()
 
 
 # ------------------------------------------------------------------ bit-pattern helpers

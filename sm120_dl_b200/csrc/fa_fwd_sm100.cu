@@ -50,7 +50,7 @@ struct FaTraits {
     static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
     static constexpr int kBoxes = D / 64;
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a Q tile, a K block or a V block
-    static constexpr int kNumBarriers = 1 + 2 * STAGES + 2 + 2;
+    static constexpr int kNumBarriers = 1 + 2 * STAGES + 2 + 4;
     static constexpr int kSmemBytes = (kQTiles + STAGES) * kTileBytes + kNumBarriers * 8 + 16 + 1024;
     static constexpr int kTmemCols = 512;
     static constexpr int kColS = 0;
@@ -69,7 +69,72 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     return r;
 }
 
-template <int D, int STAGES>
+// Packed pairs of fp32 (one 64-bit register, two lanes of the FMA pipe per instruction).
+using f32x2 = unsigned long long;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+
+// 2^x for a pair, on the FMA and integer pipes instead of the SFU: x = n + f with n the
+// nearest integer (magic-number rounding) and f in [-0.5, 0.5]; 2^f by a cubic whose
+// coefficients minimise the maximum relative error on that interval (7.5e-5, below half an
+// fp16 ulp, and P is rounded to fp16 right after); 2^n by adding n to the exponent field.
+// x is clamped at -126 so the exponent cannot wrap (masked scores, -inf, become 2^-126).
+struct Exp2PolyConsts {
+    f32x2 magic, neg_magic, neg_one, c3, c2, c1, c0;
+};
+__device__ __forceinline__ Exp2PolyConsts make_exp2_poly_consts() {
+    Exp2PolyConsts k;
+    k.magic = pack2(12582912.f, 12582912.f);  // 1.5 * 2^23
+    k.neg_magic = pack2(-12582912.f, -12582912.f);
+    k.neg_one = pack2(-1.f, -1.f);
+    k.c3 = pack2(0.0551716685f, 0.0551716685f);
+    k.c2 = pack2(0.2426111251f, 0.2426111251f);
+    k.c1 = pack2(0.6932609677f, 0.6932609677f);
+    k.c0 = pack2(0.9999280572f, 0.9999280572f);
+    return k;
+}
+__device__ __forceinline__ f32x2 exp2_poly2(f32x2 x, const Exp2PolyConsts& k) {
+    float x0, x1;
+    unpack2(x, x0, x1);
+    const f32x2 xc = pack2(fmaxf(x0, -126.f), fmaxf(x1, -126.f));
+    const f32x2 xr = add2(xc, k.magic);          // integer part in the low mantissa bits
+    const f32x2 n = add2(xr, k.neg_magic);
+    const f32x2 f = fma2(n, k.neg_one, xc);      // x - n
+    f32x2 p = fma2(k.c3, f, k.c2);
+    p = fma2(p, f, k.c1);
+    p = fma2(p, f, k.c0);
+    float p0, p1, r0, r1;
+    unpack2(p, p0, p1);
+    unpack2(xr, r0, r1);
+    // exponent += n: one integer multiply-add per element (n sits in the low bits of xr;
+    // the bits of the magic constant vanish in the shift by 23)
+    p0 = __int_as_float(__float_as_int(r0) * 8388608 + __float_as_int(p0));
+    p1 = __int_as_float(__float_as_int(r1) * 8388608 + __float_as_int(p1));
+    return pack2(p0, p1);
+}
+
+template <int D, int STAGES, int EMU>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
               const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
@@ -84,8 +149,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t kv_full = q_full + 8;                  // [STAGES] TMA -> MMA
     const uint32_t kv_empty = kv_full + 8 * STAGES;       // [STAGES] MMA -> TMA
     const uint32_t s_full = kv_empty + 8 * STAGES;        // [2] MMA -> softmax: S_i (or final O_i) ready
-    const uint32_t p_full = s_full + 16;                  // [2] softmax -> MMA: P_i written, O_i rescaled
-    const uint32_t tmem_slot = p_full + 16;
+    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: half h of P_i written (and O_i rescaled)
+    const uint32_t tmem_slot = p_full + 32;
     const uint32_t abort_slot = tmem_slot + 4;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
@@ -124,7 +189,8 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + 8 * i, 1);
-            mbar_init(p_full + 8 * i, kTileQ);
+            mbar_init(p_full + 16 * i, 4);      // one arrival per softmax warp
+            mbar_init(p_full + 16 * i + 8, 4);
         }
         *abort_ptr = 0;
         fence_mbar_init();
@@ -189,11 +255,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                               smem_desc_kmajor_sw128(k_addr + off), idesc_qk, kk > 0 ? 1u : 0u);
                 }
             };
-            auto issue_pv = [&](int i, uint32_t v_addr, bool accumulate) {
+            // Half h of P V: keys [64h, 64h+64) of the block.  P: 16 keys = 8 packed columns.
+            // V: 16 key rows = 2048 bytes; the second 64-wide span of the head dimension lives
+            // one box (16 KiB) further.
+            auto issue_pv_half = [&](int i, int h, uint32_t v_addr, bool accumulate) {
 #pragma unroll
-                for (int kk = 0; kk < kTileKV / 16; ++kk) {
-                    // P: 16 keys = 8 packed columns.  V: 16 key rows = 2048 bytes; the second
-                    // 64-wide span of the head dimension lives one box (16 KiB) further.
+                for (int kk = 4 * h; kk < 4 * h + 4; ++kk) {
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
                            smem_desc_mnmajor_sw128(v_addr + kk * 2048, kBoxBytes), idesc_pv,
                            (accumulate || kk > 0) ? 1u : 0u);
@@ -231,11 +298,15 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 bool have_k = false;
                 for (int i = 0; i < 2 && ok; ++i) {
                     if (j >= nblk[i]) continue;
-                    ok = mbar_wait(guard, p_full + 8 * i, p_ph[i], 0x1230u + i);
+                    ok = mbar_wait(guard, p_full + 16 * i, p_ph[i], 0x1230u + i);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv_half(i, 0, v_addr, j > 0);
+                    ok = mbar_wait(guard, p_full + 16 * i + 8, p_ph[i], 0x1238u + i);
                     if (!ok) break;
                     p_ph[i] ^= 1u;
                     tc_fence_after();
-                    issue_pv(i, v_addr, j > 0);
+                    issue_pv_half(i, 1, v_addr, true);
                     if (j + 1 < nblk[i]) {
                         if (!have_k) {
                             ok = mbar_wait(guard, kv_full + 8 * s, ph, 0x1240u + s);
@@ -274,8 +345,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         const uint32_t t_s = tmem_base + lane_base + T::kColS + i * kTileKV;
         const uint32_t t_o = tmem_base + lane_base + T::kColO + i * D;
         const int n = nblk[i];
+        const Exp2PolyConsts poly = make_exp2_poly_consts();
         float m = -INFINITY;  // running max the accumulators are scaled to
-        float l = 0.f;        // running sum of exp2(s*scale - m*scale)
+        float l0 = 0.f, l1 = 0.f;  // running sum of exp2(s*scale - m*scale), two partial sums
         bool ok = true;
         for (int j = 0; j < n && ok; ++j) {
             ok = mbar_wait(guard, s_full + 8 * i, j & 1, 0x1300u + i);
@@ -298,18 +370,25 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                     for (int x = 0; x < 32; ++x)
                         if (col0 + c * 32 + x > limit) sr[c][x] = 0xff800000u;  // -inf
             }
-            float mblk = -INFINITY;
+            // Four independent chains (one per 32-column chunk) instead of one 64-deep chain.
+            float mc[4];
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
+            for (int c = 0; c < 4; ++c) {
+                mc[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
 #pragma unroll
-                for (int x = 0; x < 32; ++x) mblk = fmaxf(mblk, __uint_as_float(sr[c][x]));
+                for (int x = 3; x < 31; x += 2)
+                    mc[c] = max3(mc[c], __uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1]));
+                mc[c] = fmaxf(mc[c], __uint_as_float(sr[c][31]));
+            }
+            const float mblk = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
             const float m_new = fmaxf(m, mblk);
             // Rescale only when the max moved enough to matter (always on the first block).
             const bool need = (m_new - m) * scale_log2 > kRescaleLog2 || m == -INFINITY;
             if (__any_sync(0xffffffffu, need)) {
                 const float m_use = need ? m_new : m;
                 const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - m_use) * scale_log2);
-                l *= alpha;
+                l0 *= alpha;
+                l1 *= alpha;
                 m = m_use;
                 if (j > 0) {
 #pragma unroll 1
@@ -325,23 +404,42 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             }
             const float m_fin = (m == -INFINITY) ? 0.f : m;
             const float neg_m = -m_fin * scale_log2;
+            const f32x2 scale2 = pack2(scale_log2, scale_log2);
+            const f32x2 neg_m2 = pack2(neg_m, neg_m);
+            f32x2 lsum[4] = {pack2(l0, l1), pack2(0.f, 0.f), pack2(0.f, 0.f), pack2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
                 uint32_t pr[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c][x]), scale_log2, neg_m));
-                    const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c][x + 1]), scale_log2, neg_m));
-                    l += p0 + p1;
+                    const f32x2 xs = fma2(pack2(__uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1])), scale2, neg_m2);
+                    f32x2 pp;
+                    // EMU of every 4 pairs take the polynomial path, the rest the SFU.
+                    if (((x >> 1) & 3) < EMU) {
+                        pp = exp2_poly2(xs, poly);
+                    } else {
+                        float a, b;
+                        unpack2(xs, a, b);
+                        pp = pack2(fast_exp2(a), fast_exp2(b));
+                    }
+                    lsum[c] = add2(lsum[c], pp);
+                    float p0, p1;
+                    unpack2(pp, p0, p1);
                     pr[x >> 1] = pack_f16x2(p0, p1);
                 }
                 // 32 keys = 16 packed columns; S is already in registers, so P may overwrite it.
                 tmem_st_32x32b_x16(t_s + c * 16, pr);
+                if (c & 1) {
+                    // Half of P is in tensor memory: let the MMA warp start on it.
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(p_full + 16 * i + 8 * (c >> 1));
+                }
             }
-            tmem_wait_st();
-            tc_fence_before();
-            mbar_arrive(p_full + 8 * i);
+            unpack2(add2(add2(lsum[0], lsum[1]), add2(lsum[2], lsum[3])), l0, l1);
         }
+        const float l = l0 + l1;
         if (ok && n > 0) {
             // ------------------------------------------------------------------ epilogue
             ok = mbar_wait(guard, s_full + 8 * i, n & 1, 0x1310u + i);
@@ -408,12 +506,12 @@ int make_tmap(CUtensorMap* out, const void* base, int batch, int seq, int heads,
     return encode_tmap_2byte(out, base, 4, dims, sb, box, true);
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, int EMU>
 int launch_fa(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
               void* o, int batch, int seq_q, int seq_k, int heads, const int64_t* qs, const int64_t* ks,
               const int64_t* vs, const int64_t* os, float softmax_scale, int causal, cudaStream_t stream) {
     using T = FaTraits<D, STAGES>;
-    auto kernel = fa_fwd_kernel<D, STAGES>;
+    auto kernel = fa_fwd_kernel<D, STAGES, EMU>;
     CUtensorMap tq, tk, tv, to;
     if (int rc = make_tmap(&tq, q, batch, seq_q, heads, D, qs)) return rc;
     if (int rc = make_tmap(&tk, k, batch, seq_k, heads, D, ks)) return rc;
@@ -444,10 +542,10 @@ struct FaEntry {
     FaLaunchFn launch;
 };
 
-#define B200_FA_CONFIG(NAME, D, STAGES, BLOCK_M, BLOCK_N)                                                    \
+#define B200_FA_CONFIG(NAME, D, STAGES, EMU, BLOCK_M, BLOCK_N)                                               \
     FaEntry{b200_fa_config{NAME, D, BLOCK_M, BLOCK_N, kTileQ, kQTiles, kTileKV, STAGES, kFaThreads / 32,      \
                            FaTraits<D, STAGES>::kSmemBytes},                                                 \
-            &launch_fa<D, STAGES>},
+            &launch_fa<D, STAGES, EMU>},
 
 const FaEntry kFaEntries[] = {
 #include "generated/flash_configs.inc"

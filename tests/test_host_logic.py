@@ -64,8 +64,9 @@ def test_flash_generator_rules(monkeypatch, tmp_path):
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     cfgs = f.generate_configs(227)
     assert {c[1] for c in cfgs} == {64, 128}
-    for name, hd, stages, bm, bn in cfgs:
+    for name, hd, stages, emu, bm, bn in cfgs:
         assert f.smem_bytes(hd, stages) <= 227 * 1024 and f.tmem_columns(hd) <= 512 and stages >= 3
+        assert 0 <= emu <= 3 and name == f.config_name(hd, stages, emu)
     assert not f.is_valid_config(128, 6, 227 * 1024)   # 8 x 32 KiB tiles do not fit
     assert not f.is_valid_config(256, 3, 227 * 1024)
     # the environment inputs of the reference generator still work

@@ -64,6 +64,18 @@ int b200_gemm_default_config(int M, int N, int K);
 int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                       int64_t ldb, void* C, int64_t ldc, void* stream);
 
+/* The same GEMM with its result written to n_dst (1..8) destinations: C_list[d] points at the
+ * [M,N] window (leading dimension ldc, the same for all) this call owns inside destination
+ * d.  Destinations may be on other GPUs of the box (peer-mapped memory): the epilogue stores
+ * every finished tile to all of them with TMA over NVLink, so an N-column shard lands in
+ * every rank's full-width C while the rest of the GEMM is still running, and no separate
+ * all-gather or un-permute copy is needed.  The caller synchronises the ranks afterwards.
+ * No counterpart in the reference (it is single-GPU); it replaces the NCCL all-gather the
+ * benchmark configuration allows "when the caller needs the full output on one rank". */
+int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, int64_t lda,
+                              const void* B, int64_t ldb, void* const* C_list, int n_dst, int64_t ldc,
+                              void* stream);
+
 /* Same computation, arguments and result as b200_gemm_bf16_tn, for callers that must not
  * allocate device memory: code running after a framework has reserved the whole GPU for its
  * own pool, services with a fixed memory budget that forbid allocation once they are

@@ -34,6 +34,14 @@ constexpr int kEpiWarps = 4;
 constexpr int kEpiBoxRows = 32;
 constexpr int kEpiBoxBytes = kEpiBoxRows * 128;  // 4 KiB: 32 rows x 64 bf16
 constexpr int kThreads = 32 * (2 + kEpiWarps);
+constexpr int kMaxDst = 8;                  // copies of C one launch can write (one per GPU of a box)
+
+// Tensor maps of every destination of C.  With one entry this is the plain GEMM; with several,
+// each finished box is stored to all of them (own memory and peers' memory over NVLink), which
+// is how a column shard lands in every rank's full-width C without a separate all-gather.
+struct CMapSet {
+    CUtensorMap m[kMaxDst];
+};
 
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
@@ -72,7 +80,7 @@ template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
-                    const __grid_constant__ CUtensorMap tmap_c, int M, int N, int K, int bs_w,
+                    const __grid_constant__ CMapSet tmap_c, int n_dst, int M, int N, int K, int bs_w,
                     uint32_t* status) {
     using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
     constexpr int BM = kCtaM * CTA_GROUP;
@@ -115,7 +123,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         fence_mbar_init();
         prefetch_tensormap(&tmap_a);
         prefetch_tensormap(&tmap_b);
-        prefetch_tensormap(&tmap_c);
+        for (int d = 0; d < n_dst; ++d) prefetch_tensormap(&tmap_c.m[d]);
     }
     if (warp == 1) {
         tmem_alloc<CTA_GROUP>(tmem_slot, T::kTmemCols);
@@ -279,7 +287,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) {
-                    tma_store_2d(&tmap_c, box, tn * BN + c * 64, out_row);
+                    for (int d = 0; d < n_dst; ++d) tma_store_2d(&tmap_c.m[d], box, tn * BN + c * 64, out_row);
                     tma_store_commit();
                 }
                 ++stores;
@@ -308,16 +316,18 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 // ------------------------------------------------------------------------- host launcher
 using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
-                         int64_t, const void*, int64_t, void*, int64_t, cudaStream_t);
+                         int64_t, const void*, int64_t, void* const*, int, int64_t, cudaStream_t);
 
 template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
 int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N, int K,
-                const void* A, int64_t lda, const void* B, int64_t ldb, void* C, int64_t ldc,
-                cudaStream_t stream) {
+                const void* A, int64_t lda, const void* B, int64_t ldb, void* const* C_list, int n_dst,
+                int64_t ldc, cudaStream_t stream) {
     using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
     auto kernel = gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC_BUFS>;
 
-    CUtensorMap tmap_a, tmap_b, tmap_c;
+    CUtensorMap tmap_a, tmap_b;
+    CMapSet tmap_c;
+    std::memset(&tmap_c, 0, sizeof(tmap_c));
     {
         const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
         const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
@@ -334,7 +344,9 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
         const uint64_t dims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(M)};
         const uint64_t strides[1] = {static_cast<uint64_t>(ldc) * 2};
         const uint32_t box[2] = {64, kEpiBoxRows};
-        if (int rc = encode_tmap_2byte(&tmap_c, C, 2, dims, strides, box, true)) return rc;
+        for (int d = 0; d < n_dst; ++d) {
+            if (int rc = encode_tmap_2byte(&tmap_c.m[d], C_list[d], 2, dims, strides, box, true)) return rc;
+        }
     }
 
     // Set once per (kernel, device); the reference sets it on every call
@@ -363,7 +375,7 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, M, N, K, cfg.bs_w, dev->status);
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, n_dst, M, N, K, cfg.bs_w, dev->status);
     if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
     return B200_OK;
 }
@@ -506,7 +518,34 @@ int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t ld
         return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
                     dev->max_smem_optin);
     }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C, ldc, static_cast<cudaStream_t>(stream));
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                              int64_t ldb, void* const* C_list, int n_dst, int64_t ldc, void* stream) {
+    using namespace b200;
+    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
+    const Entry& e = kEntries[config];
+    if (A == nullptr || B == nullptr || C_list == nullptr) return fail(B200_EINVAL, "null matrix pointer");
+    if (n_dst < 1 || n_dst > kMaxDst) return fail(B200_EINVAL, "n_dst must be 1..%d (got %d)", kMaxDst, n_dst);
+    for (int d = 0; d < n_dst; ++d)
+        if (C_list[d] == nullptr) return fail(B200_EINVAL, "destination %d is null", d);
+    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
+    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
+        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
+                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
+    }
+    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
+        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
+                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
+    }
+    const DeviceInfo* dev = current_device();
+    if (dev == nullptr) return B200_ENODEVICE;
+    if (e.cfg.smem_bytes > dev->max_smem_optin) {
+        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
+                    dev->max_smem_optin);
+    }
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, static_cast<cudaStream_t>(stream));
 }
 
 int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
@@ -540,7 +579,7 @@ int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, in
     // for this launch's record.  Ordered on the caller's stream, ahead of the kernel.
     cudaError_t ce = cudaMemsetAsync(dev->status, 0, kStatusBlockBytes, static_cast<cudaStream_t>(stream));
     if (ce != cudaSuccess) return fail(B200_ECUDA, "clearing the scratch block failed: %s", cudaGetErrorString(ce));
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C, ldc, static_cast<cudaStream_t>(stream));
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -69,6 +69,30 @@ def gemm_bf16_tn(a, b, out=None, config=None):
     return out
 
 
+def gemm_bf16_tn_scatter(a, b, outs, config=None):
+    """C = A @ B^T written to every tensor in `outs` (1..8 [M,N] windows with one common
+    leading dimension; they may alias other GPUs' memory, e.g. symmetric-memory buffers)."""
+    _check_matrix(a, "a", torch.bfloat16)
+    _check_matrix(b, "b", torch.bfloat16)
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    if not 1 <= len(outs) <= 8:
+        raise ValueError("between 1 and 8 destinations are supported")
+    for t in outs:
+        _check_matrix(t, "out", torch.bfloat16)
+        if tuple(t.shape) != (M, N) or t.stride(0) != outs[0].stride(0):
+            raise ValueError("every destination must be an [M,N] window with the same leading dimension")
+    idx = gemm_config_index(config, M, N, K)
+    ptrs = (ctypes.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
+    with torch.cuda.device(a.device):
+        capi.check(capi.lib().b200_gemm_bf16_tn_scatter(
+            idx, M, N, K, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), ptrs, len(outs),
+            outs[0].stride(0), _stream_ptr(a.device)))
+    return outs
+
+
 def _check_bshd(t, name):
     if not t.is_cuda:
         raise ValueError(f"{name} must be a CUDA tensor")

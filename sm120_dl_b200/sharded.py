@@ -6,6 +6,10 @@ compute, an optional all-gather of the output when the caller wants it whole.
              C[:, n0:n1].
   attention  by heads: rank r owns heads [h0, h1) of every batch; the sequence stays whole.
 
+Two ways to leave the whole output on every rank: all-gather after the kernel
+(`gather=True`), or `gemm_column_shard_fused`, where the GEMM epilogue itself stores each
+finished tile into every rank's C over NVLink (peer-mapped symmetric memory).
+
 The reference has no multi-GPU code (both of its launchers even query device 0 for the SM
 count, gemm/gemm_cute.hpp:343-346, flashattention/v3_mMnNkN/flashatten_v3.hpp:565-567);
 this module is new.  Collectives go through torch.distributed (NCCL over NVLink on GPUs;
@@ -77,6 +81,39 @@ def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None,
         for r, (s, e) in enumerate(sizes):
             full[:, s:e].copy_(staging[r, :, :e - s])
     return full, (n0, n1)
+
+
+def symmetric_empty(shape, dtype, device, group=None):
+    """A tensor every rank of `group` can address on every other rank (torch symmetric
+    memory: peer-mapped over NVLink).  Collective.  Returns (local tensor, handle)."""
+    import torch.distributed._symmetric_memory as symm_mem
+    t = symm_mem.empty(*shape, dtype=dtype, device=device)
+    handle = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+    return t, handle
+
+
+def gemm_column_shard_fused(a, b, c_full, handle, granule=256, config=None, sync=True):
+    """C = A @ B^T split by N-column blocks, with the gather fused into the GEMM's epilogue.
+
+    `c_full` [M,N] and `handle` come from symmetric_empty(); each rank's kernel stores every
+    finished tile of its column slab into ALL ranks' copies of c_full (TMA stores to peer
+    memory), so when the ranks have synchronised every copy holds the full C -- no
+    all-gather, no staging buffer, no un-permute copy.  With sync=True the call ends with a
+    barrier over the group on the current stream; a caller that reuses c_full must also
+    keep readers of the previous contents ahead of the next call (same barrier).
+    """
+    from . import ops
+    world, rank = handle.world_size, handle.rank
+    M, N = c_full.shape
+    n0, n1 = shard_bounds(N, world, rank, granule)
+    if n1 > n0:
+        outs = [handle.get_buffer(r, (M, N), c_full.dtype)[:, n0:n1] for r in range(world)]
+        # own copy first: local stores start draining while the peer maps are touched
+        outs = outs[rank:] + outs[:rank]
+        ops.gemm_bf16_tn_scatter(a, b[n0:n1], outs, config=config)
+    if sync:
+        handle.barrier()
+    return c_full, (n0, n1)
 
 
 def attention_head_shard(q, k, v, causal=False, group=None, gather=False, compute=None, config=None):

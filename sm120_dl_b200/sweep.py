@@ -13,7 +13,8 @@ Workloads (seeded synthetic operands):
 Every rank times its shard with CUDA events (5 warm-up + `iterations` launches, the
 reference harnesses' protocol); the job time is the maximum over ranks, the aggregate rate
 is the WHOLE problem's flops divided by it.  A second figure includes the NCCL all-gather
-that leaves the full output on every rank.  One JSON line per (workload, world size) is
+that leaves the full output on every rank; a third (GEMM) uses the fused variant, where the
+epilogue stores every tile into all ranks' C over NVLink and only a barrier follows.  One JSON line per (workload, world size) is
 printed by rank 0 and appended to --out; lines already present there are skipped, so an
 interrupted sweep resumes where it stopped.
 """
@@ -68,10 +69,22 @@ def run_gemm(M, N, K, world, rank, dev, iterations):
         gather_ms = timed(lambda: sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg), iterations)
         full, _ = sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg)
         assert torch.equal(full[:, n0:n1].view(torch.int16), slab.view(torch.int16)), "gathered C differs from the shard"
+    fused_ms = None
+    if world > 1:
+        c_sym, handle = sharded.symmetric_empty((M, N), torch.bfloat16, dev)
+        c_sym.fill_(float("nan"))
+        handle.barrier()
+        fused_ms = timed(lambda: sharded.gemm_column_shard_fused(a, b, c_sym, handle, granule=256, config=cfg),
+                         iterations)
+        torch.cuda.synchronize()
+        handle.barrier()
+        assert torch.equal(c_sym.view(torch.int16), full.view(torch.int16)), "fused gather differs from all-gather"
+        del c_sym, handle
     assert capi.device_status() == 0
     flops = 2.0 * M * N * K
     return {"workload": f"gemm_bf16 M={M} N={N} K={K}", "flops": flops, "kernel_config": capi.gemm_configs()[cfg]["name"],
-            "shard": f"columns [{n0},{n1}) of {N}", "compute_ms": compute_ms, "gather_ms": gather_ms}
+            "shard": f"columns [{n0},{n1}) of {N}", "compute_ms": compute_ms, "gather_ms": gather_ms,
+            "fused_ms": fused_ms}
 
 
 def run_attention(world, rank, dev, iterations):
@@ -93,7 +106,7 @@ def run_attention(world, rank, dev, iterations):
     flops = 4.0 * B * H * S * S * D
     return {"workload": f"fa_fwd_fp16 B={B} H={H} S={S} D={D}", "flops": flops,
             "kernel_config": capi.fa_configs()[cfg]["name"], "shard": f"heads [{h0},{h1}) of {H}",
-            "compute_ms": compute_ms, "gather_ms": gather_ms}
+            "compute_ms": compute_ms, "gather_ms": gather_ms, "fused_ms": None}
 
 
 def main():
@@ -132,11 +145,14 @@ def main():
             world, rank, dev, args.iterations)
         compute_ms = max_over_ranks(rec["compute_ms"], world, dev)
         gather_ms = max_over_ranks(rec["gather_ms"], world, dev) if rec["gather_ms"] is not None else None
+        fused_ms = max_over_ranks(rec["fused_ms"], world, dev) if rec["fused_ms"] is not None else None
         if rank == 0:
             line = {"workload": rec["workload"], "n_gpus": world, "scaling": "strong",
                     "compute_ms": compute_ms, "tflops": rec["flops"] / (compute_ms * 1e-3) / 1e12,
                     "with_gather_ms": gather_ms,
                     "tflops_with_gather": rec["flops"] / (gather_ms * 1e-3) / 1e12 if gather_ms else None,
+                    "fused_gather_ms": fused_ms,
+                    "tflops_fused_gather": rec["flops"] / (fused_ms * 1e-3) / 1e12 if fused_ms else None,
                     "frac_of_nominal_2250_per_gpu": rec["flops"] / (compute_ms * 1e-3) / 1e12 / world / 2250.0,
                     "kernel_config": rec["kernel_config"], "rank0_shard": rec["shard"], "iterations": args.iterations}
             text = json.dumps(line)

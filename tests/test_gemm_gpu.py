@@ -174,3 +174,27 @@ def test_python_operator_and_streams(env):
         ops.gemm_bf16_tn(a.float(), b)
     with pytest.raises(capi.B200Error):
         ops.gemm_bf16_tn(a[:100], b)
+
+
+def test_scatter_writes_every_destination(env):
+    """The multi-destination epilogue (used to fuse the gather into the GEMM): two local
+    windows of two different full-width matrices must both receive the product."""
+    torch, capi, lib, oracle, dev = env
+    from sm120_dl_b200 import ops
+    M, N, K = 512, 512, 256
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 31)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    full = [torch.full((M, 3 * N), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(3)]
+    outs = [full[0][:, N:2 * N], full[1][:, 0:N], full[2][:, 2 * N:3 * N]]
+    ops.gemm_bf16_tn_scatter(a, b, outs)
+    assert capi.device_status() == 0
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    for t in outs:
+        _check(oracle, t.float().cpu().numpy(), ref)
+    assert torch.equal(outs[0].contiguous().view(torch.int16), outs[1].contiguous().view(torch.int16))
+    # nothing outside the windows was touched
+    assert torch.isnan(full[0][:, :N]).all() and torch.isnan(full[0][:, 2 * N:]).all()
+    with pytest.raises(ValueError):
+        ops.gemm_bf16_tn_scatter(a, b, [])
+    ptrs = (ctypes.c_void_p * 9)(*[outs[0].data_ptr()] * 9)
+    assert lib.b200_gemm_bf16_tn_scatter(0, 256, 256, 64, a.data_ptr(), 64, b.data_ptr(), 64, ptrs, 9, 256, None) == -1

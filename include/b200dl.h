@@ -133,6 +133,19 @@ int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, vo
                      const int64_t k_strides[3], const int64_t v_strides[3],
                      const int64_t o_strides[3], float softmax_scale, int causal, void* stream);
 
+/* The same attention with O written to n_dst (1..8) destinations that share o_strides:
+ * o_list[d] points at the [batch, seq_q, heads, head_dim] window this call owns inside
+ * destination d (for a head shard: the full tensor's base plus the shard's first head).
+ * Destinations may be peer-mapped memory of other GPUs; every finished tile is stored to
+ * all of them with TMA, so a head shard lands in every rank's full O without an
+ * all-gather.  The caller synchronises the ranks afterwards.  No counterpart in the
+ * reference (single-GPU). */
+int b200_fa_fwd_fp16_scatter(int config, const void* q, const void* k, const void* v, void* const* o_list,
+                             int n_dst, int batch, int seq_q, int seq_k, int heads, int head_dim,
+                             const int64_t q_strides[3], const int64_t k_strides[3],
+                             const int64_t v_strides[3], const int64_t o_strides[3], float softmax_scale,
+                             int causal, void* stream);
+
 /* ----------------------------------------------------------------------------- diagnostics */
 /* Message of the last failed call on this thread ("" if none). */
 const char* b200_last_error(void);

@@ -37,7 +37,7 @@ EXPORTS = (
     "b200_gemm_num_configs", "b200_gemm_get_config", "b200_gemm_find_config",
     "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_bf16_tn_scatter",
     "b200_fa_num_configs", "b200_fa_get_config", "b200_fa_find_config",
-    "b200_fa_default_config", "b200_fa_fwd_fp16",
+    "b200_fa_default_config", "b200_fa_fwd_fp16", "b200_fa_fwd_fp16_scatter",
     "b200_last_error", "b200_device_status", "b200_version",
 )
 
@@ -84,6 +84,10 @@ def lib():
     L.b200_fa_fwd_fp16.argtypes = [ctypes.c_int, vp, vp, vp, vp, ctypes.c_int, ctypes.c_int,
                                    ctypes.c_int, ctypes.c_int, ctypes.c_int, i64p, i64p, i64p,
                                    i64p, ctypes.c_float, ctypes.c_int, vp]
+    L.b200_fa_fwd_fp16_scatter.restype = ctypes.c_int
+    L.b200_fa_fwd_fp16_scatter.argtypes = [ctypes.c_int, vp, vp, vp, ctypes.POINTER(ctypes.c_void_p), ctypes.c_int,
+                                           ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                           i64p, i64p, i64p, i64p, ctypes.c_float, ctypes.c_int, vp]
     L.b200_last_error.restype = ctypes.c_char_p
     L.b200_device_status.restype = ctypes.c_int
     L.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]

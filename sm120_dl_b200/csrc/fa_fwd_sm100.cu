@@ -35,6 +35,7 @@ constexpr int kTileKV = 128;
 constexpr int kQTiles = 2;
 constexpr int kFaThreads = 384;
 constexpr int kBoxBytes = 128 * 128;      // one TMA box: 128 rows x 64 fp16 (128 bytes)
+constexpr int kMaxDst = 8;                // copies of O one launch can write (one per GPU of a box)
 constexpr float kRescaleLog2 = 8.0f;      // rescale O only when the max grew by > 2^8
 // Register budget after the role split.  setmaxnreg.inc blocks until the CTA's own pool
 // (registers per thread at launch x threads) can supply the increase, so the two budgets
@@ -44,6 +45,13 @@ constexpr int kRegsLoadMma = 56;          // warps 0-3
 constexpr int kRegsSoftmax = 224;         // warps 4-11
 static_assert(kRegsLoadMma * 128 + kRegsSoftmax * 256 <= kRegsAtLaunch * kFaThreads,
               "setmaxnreg budgets exceed the registers the CTA is launched with");
+
+// Tensor maps of every destination of O: one entry is plain attention; several make the
+// epilogue store each finished tile into all of them (peers' memory over NVLink included),
+// which leaves a head shard in every rank's full tensor without a separate all-gather.
+struct OMapSet {
+    CUtensorMap m[kMaxDst];
+};
 
 template <int D, int STAGES>
 struct FaTraits {
@@ -137,7 +145,7 @@ __device__ __forceinline__ f32x2 exp2_poly2(f32x2 x, const Exp2PolyConsts& k) {
 template <int D, int STAGES, int EMU>
 __global__ void __launch_bounds__(kFaThreads, 1)
 fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_o,
+              const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ OMapSet tmap_o, int n_dst,
               int seq_q, int seq_k, float scale_log2, int causal, uint32_t* status) {
     using T = FaTraits<D, STAGES>;
     extern __shared__ uint8_t smem_raw[];
@@ -197,7 +205,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_k);
         prefetch_tensormap(&tmap_v);
-        prefetch_tensormap(&tmap_o);
+        for (int d = 0; d < n_dst; ++d) prefetch_tensormap(&tmap_o.m[d]);
     }
     if (warp == 1) {
         tmem_alloc<1>(tmem_slot, T::kTmemCols);
@@ -468,8 +476,9 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 fence_proxy_async_smem();
                 named_bar_sync(1 + i, kTileQ);
                 if (row_in_tile == 0) {
-                    for (int b = 0; b < T::kBoxes; ++b)
-                        tma_store_4d(&tmap_o, stage + b * kBoxBytes, b * 64, q0 + i * kTileQ, head, batch);
+                    for (int d = 0; d < n_dst; ++d)
+                        for (int b = 0; b < T::kBoxes; ++b)
+                            tma_store_4d(&tmap_o.m[d], stage + b * kBoxBytes, b * 64, q0 + i * kTileQ, head, batch);
                     tma_store_commit();
                     tma_store_wait_all<0>();
                 }
@@ -491,7 +500,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
 
 // ------------------------------------------------------------------------- host launcher
 using FaLaunchFn = int (*)(const DeviceInfo*, const b200_fa_config&, const void*, const void*, const void*,
-                           void*, int, int, int, int, const int64_t*, const int64_t*, const int64_t*,
+                           void* const*, int, int, int, int, int, const int64_t*, const int64_t*, const int64_t*,
                            const int64_t*, float, int, cudaStream_t);
 
 // Tensor map over a [batch, seq, head, dim] tensor: dimensions innermost-first
@@ -508,15 +517,20 @@ int make_tmap(CUtensorMap* out, const void* base, int batch, int seq, int heads,
 
 template <int D, int STAGES, int EMU>
 int launch_fa(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
-              void* o, int batch, int seq_q, int seq_k, int heads, const int64_t* qs, const int64_t* ks,
+              void* const* o_list, int n_dst, int batch, int seq_q, int seq_k, int heads, const int64_t* qs,
+              const int64_t* ks,
               const int64_t* vs, const int64_t* os, float softmax_scale, int causal, cudaStream_t stream) {
     using T = FaTraits<D, STAGES>;
     auto kernel = fa_fwd_kernel<D, STAGES, EMU>;
-    CUtensorMap tq, tk, tv, to;
+    CUtensorMap tq, tk, tv;
+    OMapSet to;
+    std::memset(&to, 0, sizeof(to));
     if (int rc = make_tmap(&tq, q, batch, seq_q, heads, D, qs)) return rc;
     if (int rc = make_tmap(&tk, k, batch, seq_k, heads, D, ks)) return rc;
     if (int rc = make_tmap(&tv, v, batch, seq_k, heads, D, vs)) return rc;
-    if (int rc = make_tmap(&to, o, batch, seq_q, heads, D, os)) return rc;
+    for (int d = 0; d < n_dst; ++d) {
+        if (int rc = make_tmap(&to.m[d], o_list[d], batch, seq_q, heads, D, os)) return rc;
+    }
 
     static bool attr_done[64] = {};
     if (!attr_done[dev->device]) {
@@ -530,8 +544,8 @@ int launch_fa(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, c
     if (heads > 65535 || batch > 65535) return fail(B200_ESHAPE, "heads and batch must be <= 65535");
     const dim3 grid(static_cast<unsigned>(q_pairs), static_cast<unsigned>(heads), static_cast<unsigned>(batch));
     const float scale_log2 = softmax_scale * 1.4426950408889634f;
-    kernel<<<grid, kFaThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, seq_q, seq_k, scale_log2, causal ? 1 : 0,
-                                                        dev->status);
+    kernel<<<grid, kFaThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, n_dst, seq_q, seq_k, scale_log2,
+                                                        causal ? 1 : 0, dev->status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
     return B200_OK;
@@ -580,14 +594,17 @@ int b200_fa_default_config(int head_dim) {
     return -1;
 }
 
-int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, void* o, int batch, int seq_q,
-                     int seq_k, int heads, int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
-                     const int64_t v_strides[3], const int64_t o_strides[3], float softmax_scale, int causal,
-                     void* stream) {
+int b200_fa_fwd_fp16_scatter(int config, const void* q, const void* k, const void* v, void* const* o_list, int n_dst,
+                             int batch, int seq_q, int seq_k, int heads, int head_dim, const int64_t q_strides[3],
+                             const int64_t k_strides[3], const int64_t v_strides[3], const int64_t o_strides[3],
+                             float softmax_scale, int causal, void* stream) {
     using namespace b200;
     if (config < 0 || config >= kNumFaEntries) return fail(B200_EINVAL, "unknown attention config index %d", config);
     const FaEntry& e = kFaEntries[config];
-    if (!q || !k || !v || !o) return fail(B200_EINVAL, "null tensor pointer");
+    if (!q || !k || !v || !o_list) return fail(B200_EINVAL, "null tensor pointer");
+    if (n_dst < 1 || n_dst > kMaxDst) return fail(B200_EINVAL, "n_dst must be 1..%d (got %d)", kMaxDst, n_dst);
+    for (int d = 0; d < n_dst; ++d)
+        if (!o_list[d]) return fail(B200_EINVAL, "null tensor pointer");
     if (!q_strides || !k_strides || !v_strides || !o_strides) return fail(B200_EINVAL, "null stride array");
     if (head_dim != e.cfg.head_dim)
         return fail(B200_ESHAPE, "%s expects head_dim=%d, got %d", e.cfg.name, e.cfg.head_dim, head_dim);
@@ -603,8 +620,17 @@ int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, vo
                 return fail(B200_EINVAL, "strides must be positive multiples of 8 elements");
     const DeviceInfo* dev = current_device();
     if (dev == nullptr) return B200_ENODEVICE;
-    return e.launch(dev, e.cfg, q, k, v, o, batch, seq_q, seq_k, heads, q_strides, k_strides, v_strides,
+    return e.launch(dev, e.cfg, q, k, v, o_list, n_dst, batch, seq_q, seq_k, heads, q_strides, k_strides, v_strides,
                     o_strides, softmax_scale, causal, static_cast<cudaStream_t>(stream));
+}
+
+int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, void* o, int batch, int seq_q,
+                     int seq_k, int heads, int head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
+                     const int64_t v_strides[3], const int64_t o_strides[3], float softmax_scale, int causal,
+                     void* stream) {
+    if (!o) return b200::fail(B200_EINVAL, "null tensor pointer");
+    return b200_fa_fwd_fp16_scatter(config, q, k, v, &o, 1, batch, seq_q, seq_k, heads, head_dim, q_strides, k_strides,
+                                    v_strides, o_strides, softmax_scale, causal, stream);
 }
 
 }  // extern "C"

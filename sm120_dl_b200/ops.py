@@ -147,3 +147,28 @@ def flash_attn_fwd(q, k, v, causal=False, softmax_scale=None, out=None, config=N
             _strides3(q), _strides3(k), _strides3(v), _strides3(out), float(softmax_scale),
             int(bool(causal)), _stream_ptr(q.device)))
     return out
+
+
+def flash_attn_fwd_scatter(q, k, v, outs, causal=False, softmax_scale=None, config=None):
+    """Attention forward written to every tensor in `outs` (1..8 [B,S,H,D] windows with
+    identical strides; they may alias other GPUs' memory)."""
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_bshd(t, n)
+    B, Sq, H, D = q.shape
+    Sk = k.shape[1]
+    if not 1 <= len(outs) <= 8:
+        raise ValueError("between 1 and 8 destinations are supported")
+    for t in outs:
+        _check_bshd(t, "out")
+        if tuple(t.shape) != (B, Sq, H, D) or t.stride() != outs[0].stride():
+            raise ValueError("every destination must be a [B,S,H,D] window with the same strides")
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(D)
+    idx = fa_config_index(config, D)
+    ptrs = (ctypes.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
+    with torch.cuda.device(q.device):
+        capi.check(capi.lib().b200_fa_fwd_fp16_scatter(
+            idx, q.data_ptr(), k.data_ptr(), v.data_ptr(), ptrs, len(outs), B, Sq, Sk, H, D,
+            _strides3(q), _strides3(k), _strides3(v), _strides3(outs[0]), float(softmax_scale),
+            int(bool(causal)), _stream_ptr(q.device)))
+    return outs

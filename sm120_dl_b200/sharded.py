@@ -151,3 +151,21 @@ def attention_head_shard(q, k, v, causal=False, group=None, gather=False, comput
         for r, (s, e) in enumerate(sizes):
             full[:, :, s:e].copy_(staging[r, :, :, :e - s])
     return full, (h0, h1)
+
+
+def attention_head_shard_fused(q, k, v, o_full, handle, causal=False, config=None, sync=True):
+    """Attention with the heads split across ranks and the gather fused into the kernel's
+    epilogue: each rank stores its heads' output tiles into ALL ranks' copies of `o_full`
+    ([B,S,H,D] from symmetric_empty()).  Same synchronisation rules as
+    gemm_column_shard_fused."""
+    from . import ops
+    world, rank = handle.world_size, handle.rank
+    B, S, H, D = o_full.shape
+    h0, h1 = shard_bounds(H, world, rank)
+    if h1 > h0:
+        outs = [handle.get_buffer(r, (B, S, H, D), o_full.dtype)[:, :, h0:h1] for r in range(world)]
+        outs = outs[rank:] + outs[:rank]
+        ops.flash_attn_fwd_scatter(q[:, :, h0:h1], k[:, :, h0:h1], v[:, :, h0:h1], outs, causal=causal, config=config)
+    if sync:
+        handle.barrier()
+    return o_full, (h0, h1)

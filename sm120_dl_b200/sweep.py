@@ -13,9 +13,9 @@ Workloads (seeded synthetic operands):
 Every rank times its shard with CUDA events (5 warm-up + `iterations` launches, the
 reference harnesses' protocol); the job time is the maximum over ranks, the aggregate rate
 is the WHOLE problem's flops divided by it.  A second figure includes the NCCL all-gather
-that leaves the full output on every rank; a third (GEMM) uses the fused variant, where the
-epilogue stores every tile into all ranks' C over NVLink and only a barrier follows.  One JSON line per (workload, world size) is
-printed by rank 0 and appended to --out; lines already present there are skipped, so an
+that leaves the full output on every rank; a third uses the fused variant, where the kernel's
+epilogue stores every tile into all ranks' output over NVLink and only a barrier follows.
+One JSON line per (workload, world size) is printed by rank 0 and appended to --out; lines already present there are skipped, so an
 interrupted sweep resumes where it stopped.
 """
 
@@ -102,11 +102,21 @@ def run_attention(world, rank, dev, iterations):
         gather_ms = timed(lambda: sharded.attention_head_shard(q, k, v, gather=True, config=cfg), iterations)
         full, _ = sharded.attention_head_shard(q, k, v, gather=True, config=cfg)
         assert torch.equal(full[:, :, h0:h1].view(torch.int16), out.view(torch.int16)), "gathered O differs from the shard"
+    fused_ms = None
+    if world > 1:
+        o_sym, handle = sharded.symmetric_empty((B, S, H, D), torch.float16, dev)
+        o_sym.fill_(float("nan"))
+        handle.barrier()
+        fused_ms = timed(lambda: sharded.attention_head_shard_fused(q, k, v, o_sym, handle, config=cfg), iterations)
+        torch.cuda.synchronize()
+        handle.barrier()
+        assert torch.equal(o_sym.view(torch.int16), full.view(torch.int16)), "fused gather differs from all-gather"
+        del o_sym, handle
     assert capi.device_status() == 0
     flops = 4.0 * B * H * S * S * D
     return {"workload": f"fa_fwd_fp16 B={B} H={H} S={S} D={D}", "flops": flops,
             "kernel_config": capi.fa_configs()[cfg]["name"], "shard": f"heads [{h0},{h1}) of {H}",
-            "compute_ms": compute_ms, "gather_ms": gather_ms, "fused_ms": None}
+            "compute_ms": compute_ms, "gather_ms": gather_ms, "fused_ms": fused_ms}
 
 
 def main():

@@ -192,3 +192,22 @@ def test_module_rejections(env, module):
     with pytest.raises(RuntimeError, match="expects head_dim=64"):
         z = torch.zeros(1, 128, 2, 128, dtype=torch.float16, device=dev)
         module.fwd_config(module.configs()[0][0], z, z, z)
+
+
+def test_scatter_writes_every_destination(env):
+    """The multi-destination epilogue (used to fuse the head gather into the kernel)."""
+    torch, capi, lib, oracle, dev = env
+    from sm120_dl_b200 import ops
+    B, S, H, D = 1, 320, 2, 128
+    q_bits, k_bits, v_bits = oracle.make_fa_inputs(B, S, H, D, seed=41)
+    q, k, v = (_dev(torch, x, dev) for x in (q_bits, k_bits, v_bits))
+    full = [torch.full((B, S, 6, D), float("nan"), dtype=torch.float16, device=dev) for _ in range(2)]
+    outs = [full[0][:, :, 2:4], full[1][:, :, 2:4]]
+    ops.flash_attn_fwd_scatter(q, k, v, outs, causal=True)
+    assert capi.device_status() == 0
+    ref = oracle.attention_f32(q_bits, k_bits, v_bits, True)
+    for t in outs:
+        assert np.abs(t.float().cpu().numpy() - ref).max() <= ABS_BOUND
+    assert torch.isnan(full[0][:, :, :2]).all() and torch.isnan(full[1][:, :, 4:]).all()
+    with pytest.raises(ValueError):  # destinations of different shapes
+        ops.flash_attn_fwd_scatter(q, k, v, [full[0][:, :, 0:2], full[1][:, ::2, 0:2]])

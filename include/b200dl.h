@@ -31,8 +31,11 @@ extern "C" {
 /* ------------------------------------------------------------------ GEMM config registry
  * Replaces the generated table `kGemmConfigs[] / kGemmConfigCount` and the per-config
  * explicit instantiations of gemm_tn<> (gemm/gemm_config_registry.hpp.in:11-37,
- * gemm/gemm_config_registry.cu.in:6-10, gemm/gemm.cu.in:59-66).  A problem is legal for a
- * config when M % bm == 0, N % bn == 0 and K % bk == 0 (gemm/test.cpp:449-451). */
+ * gemm/gemm_config_registry.cu.in:6-10, gemm/gemm.cu.in:59-66).  The reference runs a config
+ * only when M % bm == 0, N % bn == 0 and K % bk == 0 (gemm/test.cpp:449-451) and its
+ * registry wrappers keep that rule; the entry points below accept any positive M and K and
+ * any positive N that is a multiple of 8 (partial tiles are zero-filled on load and
+ * clipped on store by the TMA engine; stores clip at 16-byte granularity, hence N % 8). */
 typedef struct b200_gemm_config {
     const char* name;   /* unique, e.g. "bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8"            */
     int bm;             /* output tile rows per CTA group (128 * cta_group)                  */
@@ -51,14 +54,15 @@ int b200_gemm_num_configs(void);
 const b200_gemm_config* b200_gemm_get_config(int idx);
 /* Index of the config with exactly this name, or -1. */
 int b200_gemm_find_config(const char* name);
-/* Index of the config this library would pick for the shape (largest legal tile that
- * still fills the GPU), or -1 when no built config divides the shape. */
+/* Index of the config this library would pick for the shape (largest tile that still
+ * fills the GPU, discounted by the work wasted on ragged edges), or -1 for a non-positive
+ * shape. */
 int b200_gemm_default_config(int M, int N, int K);
 
 /* C[M,N] = A[M,K] * B[N,K]^T, bf16 operands, fp32 accumulation, bf16 round-to-nearest-even
  * output, C fully overwritten (alpha = 1, beta = 0).  Row-major with leading dimensions
- * lda, ldb, ldc in ELEMENTS (each a multiple of 8; the reference has none and means
- * lda = ldb = K, ldc = N).  Replaces gemm_tn<T,BM,BN,BK,STAGE,CWG,WARPS_M,WARPS_N,BS_W>
+ * lda, ldb, ldc in ELEMENTS (each a multiple of 8 and at least the row length; the reference
+ * has none and means lda = ldb = K, ldc = N).  M, N, K need not be multiples of the tile (N % 8 == 0).  Replaces gemm_tn<T,BM,BN,BK,STAGE,CWG,WARPS_M,WARPS_N,BS_W>
  * (gemm/gemm_cute.hpp:268-356) and the kernel b16_gemm (gemm/gemm_cute.hpp:64-266); the
  * leading dimensions exist so an N-column shard can write its slab of a full-width C. */
 int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,

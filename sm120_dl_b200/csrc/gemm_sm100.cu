@@ -138,10 +138,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot_ptr;
 
-    const int tiles_m = M / BM;
-    const int tiles_n = N / BN;
+    // Ragged edges cost nothing extra: TMA zero-fills loads past the end of a matrix (zero
+    // rows and zero k-columns add nothing) and clips stores.
+    const int tiles_m = (M + BM - 1) / BM;
+    const int tiles_n = (N + BN - 1) / BN;
     const int num_tiles = tiles_m * tiles_n;
-    const int k_blocks = K / kBK;
+    const int k_blocks = (K + kBK - 1) / kBK;
     const int group = blockIdx.x / CTA_GROUP;
     const int num_groups = gridDim.x / CTA_GROUP;
 
@@ -359,7 +361,7 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
         attr_done[dev->device] = true;
     }
 
-    const int num_tiles = (M / (kCtaM * CTA_GROUP)) * (N / BN);
+    const int num_tiles = ((M + kCtaM * CTA_GROUP - 1) / (kCtaM * CTA_GROUP)) * ((N + BN - 1) / BN);
     int groups = dev->sm_count / CTA_GROUP;
     if (groups > num_tiles) groups = num_tiles;
 
@@ -479,16 +481,19 @@ int b200_gemm_default_config(int M, int N, int K) {
     long best_score = -1;
     for (int i = 0; i < b200::kNumEntries; ++i) {
         const b200_gemm_config& c = b200::kEntries[i].cfg;
-        if (M <= 0 || N <= 0 || K <= 0 || M % c.bm || N % c.bn || K % c.bk) continue;
-        const long tiles = static_cast<long>(M / c.bm) * (N / c.bn);
+        if (M <= 0 || N <= 0 || K <= 0) continue;
+        const long tiles = static_cast<long>((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+        // work wasted on the ragged edge counts against a large tile
+        const double useful = static_cast<double>(M) * N / (static_cast<double>(tiles) * c.bm * c.bn);
         const long ctas = tiles * c.cta_group;
-        const long area = static_cast<long>(c.bm) * c.bn;
+        const long area = static_cast<long>(static_cast<double>(c.bm) * c.bn * useful);
         // Enough tiles to occupy 148 SMs: largest tile, then deepest ring, strip width 8
         // (fastest measured on 8192^3).  Otherwise: most SMs busy, single-CTA MMA first
         // (no pair synchronisation to pay for on a latency-bound problem), then larger tile.
         const long score = (ctas >= 148)
                                ? (1000000000L + area * 64 + c.stages * 4 + (c.bs_w == 8 ? 2 : 0) + c.cta_group)
-                               : (ctas * 100000L + (c.cta_group == 1 ? 50000L : 0L) + area / 64 + c.stages);
+                               : (static_cast<long>(ctas * useful * 1000.0) * 1000L + (c.cta_group == 1 ? 500L : 0L) +
+                                  area / 1024 + c.stages);
         if (score > best_score) {
             best_score = score;
             best = i;
@@ -504,10 +509,7 @@ int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t ld
     const Entry& e = kEntries[config];
     if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
     if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
-        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
-                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
-    }
+    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
     if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
         return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
                     static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
@@ -531,10 +533,7 @@ int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, in
     for (int d = 0; d < n_dst; ++d)
         if (C_list[d] == nullptr) return fail(B200_EINVAL, "destination %d is null", d);
     if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
-        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
-                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
-    }
+    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
     if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
         return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
                     static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
@@ -555,10 +554,7 @@ int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, in
     const Entry& e = kEntries[config];
     if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
     if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (M % e.cfg.bm != 0 || N % e.cfg.bn != 0 || K % e.cfg.bk != 0) {
-        return fail(B200_ESHAPE, "%s: shape %dx%dx%d is not divisible by the tile %dx%dx%d", e.cfg.name, M, N, K,
-                    e.cfg.bm, e.cfg.bn, e.cfg.bk);
-    }
+    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
     if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
         return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
                     static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));

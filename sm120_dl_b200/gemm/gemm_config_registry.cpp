@@ -16,6 +16,13 @@ namespace {
 
 template <int Index>
 void run_config(int M, int N, int K, const bf16* A, const bf16* B, bf16* C, cudaStream_t stream) {
+    // The reference's gemm_tn refuses shapes its tile does not divide (gemm/gemm_cute.hpp:288-291).
+    const b200_gemm_config* cfg = b200_gemm_get_config(Index);
+    if (cfg == nullptr || M % cfg->bm != 0 || N % cfg->bn != 0 || K % cfg->bk != 0) {
+        std::fprintf(stderr, "gemm_tn: M=%d N=%d K=%d must be multiples of BM=%d BN=%d BK=%d\n", M, N, K,
+                     cfg ? cfg->bm : 0, cfg ? cfg->bn : 0, cfg ? cfg->bk : 0);
+        std::exit(1);
+    }
     const int rc = b200_gemm_bf16_tn(Index, M, N, K, A, K, B, K, C, N, stream);
     if (rc != B200_OK) {
         std::fprintf(stderr, "gemm_tn config %d failed (%d): %s\n", Index, rc, b200_last_error());

@@ -146,12 +146,37 @@ def test_config2_8192_cubed_rows_and_linearity(env):
     assert np.abs(col_sums - expect).max() <= 2e-3 * np.sqrt(n) * c.float().abs().max().item()
 
 
+@pytest.mark.parametrize("shape", [(300, 200, 100), (129, 264, 65), (1000, 72, 520), (1, 8, 8)])
+def test_shapes_no_tile_divides(env, shape):
+    """Ragged M, N and K (the reference refuses these; here TMA zero-fills and clips).  The
+    rows are padded to a multiple of 8 elements and the padding is poisoned."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = shape
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 50 + M)
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    lda = ldb = (K + 7) // 8 * 8
+    ldc = (N + 7) // 8 * 8
+    a = torch.full((M, lda), float("nan"), dtype=torch.bfloat16, device=dev)
+    b = torch.full((N, ldb), float("nan"), dtype=torch.bfloat16, device=dev)
+    a[:, :K] = _to_dev(torch, a_bits, dev, torch.bfloat16)
+    b[:, :K] = _to_dev(torch, b_bits, dev, torch.bfloat16)
+    for name in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn64_bk64_s8_cta1_acc2_bsw8", None):
+        idx = lib.b200_gemm_default_config(M, N, K) if name is None else lib.b200_gemm_find_config(name.encode())
+        c = torch.full((M + 3, ldc), 7.0, dtype=torch.bfloat16, device=dev)
+        _run(env, idx, a, b, M, N, K, c=c, lda=lda, ldb=ldb, ldc=ldc)
+        _check(oracle, c[:M, :N].float().cpu().numpy(), ref)
+        assert (c[M:] == 7.0).all() and (c[:, N:] == 7.0).all(), "stores leaked past the edge of C"
+
+
 def test_error_paths(env):
     torch, capi, lib, oracle, dev = env
     a = torch.zeros(256, 64, dtype=torch.bfloat16, device=dev)
     idx = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
-    assert lib.b200_gemm_bf16_tn(idx, 256, 128, 64, a.data_ptr(), 64, a.data_ptr(), 64, a.data_ptr(), 128, None) == -2
-    assert b"not divisible" in lib.b200_last_error()
+    assert lib.b200_gemm_bf16_tn(idx, 256, 0, 64, a.data_ptr(), 64, a.data_ptr(), 64, a.data_ptr(), 128, None) == -2
+    assert b"must be positive" in lib.b200_last_error()
+    assert lib.b200_gemm_bf16_tn(idx, 256, 128, 64, a.data_ptr(), 60, a.data_ptr(), 64, a.data_ptr(), 128, None) == -1
+    assert lib.b200_gemm_bf16_tn(idx, 256, 132, 64, a.data_ptr(), 64, a.data_ptr(), 64, a.data_ptr(), 136, None) == -2
+    assert b"multiple of 8" in lib.b200_last_error()
     # a base pointer that is not 16-byte aligned cannot be described to the TMA engine
     assert lib.b200_gemm_bf16_tn(idx, 256, 256, 64, a.data_ptr() + 2, 64, a.data_ptr(), 64, a.data_ptr(), 256, None) == -1
     assert b"aligned" in lib.b200_last_error()
@@ -173,7 +198,9 @@ def test_python_operator_and_streams(env):
     with pytest.raises(ValueError):
         ops.gemm_bf16_tn(a.float(), b)
     with pytest.raises(capi.B200Error):
-        ops.gemm_bf16_tn(a[:100], b)
+        ops.gemm_bf16_tn(a, b[:100])          # N = 100 is not a multiple of 8
+    c100 = ops.gemm_bf16_tn(a[:100], b)       # a ragged M is fine
+    _check(oracle, c100.float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits)[:100])
 
 
 def test_scatter_writes_every_destination(env):

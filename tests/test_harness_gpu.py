@@ -70,3 +70,9 @@ def test_verify_host_mode(exe):
     p = _run(exe, "--verify-host", "512", "512", "512")
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert "verify-host success" in p.stdout and "failed" not in p.stdout
+
+
+def test_registry_run_still_refuses_shapes_its_tile_does_not_divide(exe):
+    """The C ABI accepts ragged shapes, the reference-shaped registry keeps gemm_tn's rule."""
+    p = _run(exe, "--profile", "bf16_bm128_bn64_bk64_s8_cta1_acc2_bsw8", "130", "64", "64")
+    assert p.returncode != 0 and "profile skipped:" in p.stdout

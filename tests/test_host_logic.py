@@ -114,13 +114,14 @@ def test_config_lookup(lib):
     first = lib.b200_gemm_get_config(0).contents.name
     assert lib.b200_gemm_find_config(first) == 0
     assert not lib.b200_gemm_get_config(-1) and not lib.b200_gemm_get_config(10 ** 6)
-    # 8192^3 gets a 256x256 CTA-pair tile; 512^3 a small tile that spreads over more SMs;
-    # a shape no tile divides gets nothing
+    # 8192^3 gets a 256x256 CTA-pair tile; 512^3 a small tile that spreads over more SMs
     big = lib.b200_gemm_get_config(lib.b200_gemm_default_config(8192, 8192, 8192)).contents
     assert (big.bm, big.bn, big.cta_group) == (256, 256, 2)
     small = lib.b200_gemm_get_config(lib.b200_gemm_default_config(512, 512, 512)).contents
     assert small.bn == 64 and small.cta_group == 1
-    assert lib.b200_gemm_default_config(100, 100, 100) == -1
+    ragged = lib.b200_gemm_get_config(lib.b200_gemm_default_config(100, 100, 100)).contents
+    assert ragged.bm == 128 and ragged.bn == 64      # a ragged shape gets the tile that wastes least
+    assert lib.b200_gemm_default_config(0, 100, 100) == -1
     for hd in (64, 128):
         idx = lib.b200_fa_default_config(hd)
         assert lib.b200_fa_get_config(idx).contents.head_dim == hd
@@ -134,8 +135,8 @@ def test_argument_errors_need_no_gpu(lib):
     assert lib.b200_gemm_bf16_tn(999, 256, 256, 64, 8, 64, 8, 64, 8, 256, None) == -1
     assert b"unknown GEMM config" in lib.b200_last_error()
     assert lib.b200_gemm_bf16_tn(0, 256, 256, 64, None, 64, None, 64, None, 256, None) == -1
-    assert lib.b200_gemm_bf16_tn(0, 250, 256, 64, 8, 64, 8, 64, 8, 256, None) == -2
-    assert b"not divisible" in lib.b200_last_error()
+    assert lib.b200_gemm_bf16_tn(0, 0, 256, 64, 8, 64, 8, 64, 8, 256, None) == -2
+    assert b"must be positive" in lib.b200_last_error()
     assert lib.b200_gemm_bf16_tn(0, 256, 256, 64, 8, 60, 8, 64, 8, 256, None) == -1   # lda < K
     st = (ctypes.c_int64 * 3)(64 * 64, 64, 64)
     idx = lib.b200_fa_default_config(64)

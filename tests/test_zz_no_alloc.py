@@ -62,7 +62,7 @@ def test_noalloc_rejects_bad_arguments(cuda_device):
     lib = capi.lib()
     x = torch.zeros(256, 256, dtype=torch.bfloat16, device=cuda_device)
     cfg = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
-    assert lib.b200_gemm_bf16_tn_noalloc(cfg, 200, 256, 256, x.data_ptr(), 256, x.data_ptr(), 256, x.data_ptr(), 256, None) == -2
-    assert b"not divisible" in lib.b200_last_error()
+    assert lib.b200_gemm_bf16_tn_noalloc(cfg, 0, 256, 256, x.data_ptr(), 256, x.data_ptr(), 256, x.data_ptr(), 256, None) == -2
+    assert b"must be positive" in lib.b200_last_error()
     assert lib.b200_gemm_bf16_tn_noalloc(-1, 256, 256, 256, x.data_ptr(), 256, x.data_ptr(), 256, x.data_ptr(), 256, None) == -1
     assert lib.b200_gemm_bf16_tn_noalloc(cfg, 256, 256, 256, None, 256, x.data_ptr(), 256, x.data_ptr(), 256, None) == -1

@@ -68,6 +68,12 @@ int b200_gemm_default_config(int M, int N, int K);
 int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                       int64_t ldb, void* C, int64_t ldc, void* stream);
 
+/* The same GEMM for fp16 operands and fp16 output (fp32 accumulation).  The reference's
+ * kernel template admits cutlass::half_t (gemm/gemm_cute.hpp:279-280) although its
+ * generator only instantiates bf16 (gemm/gemm_configs.py:11-13). */
+int b200_gemm_f16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                     int64_t ldb, void* C, int64_t ldc, void* stream);
+
 /* The same GEMM with its result written to n_dst (1..8) destinations: C_list[d] points at the
  * [M,N] window (leading dimension ldc, the same for all) this call owns inside destination
  * d.  Destinations may be on other GPUs of the box (peer-mapped memory): the epilogue stores

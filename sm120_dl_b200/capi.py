@@ -35,7 +35,7 @@ class FaConfig(ctypes.Structure):
 
 EXPORTS = (
     "b200_gemm_num_configs", "b200_gemm_get_config", "b200_gemm_find_config",
-    "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_bf16_tn_scatter",
+    "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_f16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_bf16_tn_scatter",
     "b200_fa_num_configs", "b200_fa_get_config", "b200_fa_find_config",
     "b200_fa_default_config", "b200_fa_fwd_fp16", "b200_fa_fwd_fp16_scatter",
     "b200_last_error", "b200_device_status", "b200_version",
@@ -66,6 +66,8 @@ def lib():
     L.b200_gemm_bf16_tn.restype = ctypes.c_int
     L.b200_gemm_bf16_tn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                     vp, i64, vp, i64, vp, i64, vp]
+    L.b200_gemm_f16_tn.restype = ctypes.c_int
+    L.b200_gemm_f16_tn.argtypes = L.b200_gemm_bf16_tn.argtypes
     L.b200_gemm_bf16_tn_scatter.restype = ctypes.c_int
     L.b200_gemm_bf16_tn_scatter.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, i64, vp, i64,
                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, i64, vp]

@@ -81,6 +81,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CMapSet tmap_c, int n_dst, int M, int N, int K, int bs_w,
+                    int is_bf16,
                     uint32_t* status) {
     using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
     constexpr int BM = kCtaM * CTA_GROUP;
@@ -194,7 +195,8 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if (warp == 1) {
         // -------------------------------------------------------------------- MMA issuer
         if (lane == 0 && is_leader) {
-            constexpr uint32_t idesc = make_idesc_f16(BM, BN, /*bf16*/ 1, 0, 0);
+            // operand format: bf16 (1) or fp16 (0); the accumulator is fp32 either way
+            const uint32_t idesc = make_idesc_f16(BM, BN, is_bf16 ? 1 : 0, 0, 0);
             int s = 0;
             uint32_t ph = 0;
             uint32_t local_tile = 0;
@@ -269,12 +271,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 uint32_t packed[32];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    __nv_bfloat162 v0 = __floats2bfloat162_rn(__uint_as_float(acc0[2 * i]),
-                                                              __uint_as_float(acc0[2 * i + 1]));
-                    __nv_bfloat162 v1 = __floats2bfloat162_rn(__uint_as_float(acc1[2 * i]),
-                                                              __uint_as_float(acc1[2 * i + 1]));
-                    packed[i] = *reinterpret_cast<uint32_t*>(&v0);
-                    packed[16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                    const float a0 = __uint_as_float(acc0[2 * i]), a1 = __uint_as_float(acc0[2 * i + 1]);
+                    const float b0 = __uint_as_float(acc1[2 * i]), b1 = __uint_as_float(acc1[2 * i + 1]);
+                    if (is_bf16) {
+                        __nv_bfloat162 v0 = __floats2bfloat162_rn(a0, a1);
+                        __nv_bfloat162 v1 = __floats2bfloat162_rn(b0, b1);
+                        packed[i] = *reinterpret_cast<uint32_t*>(&v0);
+                        packed[16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                    } else {
+                        __half2 v0 = __floats2half2_rn(a0, a1);
+                        __half2 v1 = __floats2half2_rn(b0, b1);
+                        packed[i] = *reinterpret_cast<uint32_t*>(&v0);
+                        packed[16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                    }
                 }
                 const uint32_t box = my_epi + (stores & 1u) * kEpiBoxBytes;
                 // The store issued two steps ago read this box; wait until it has.
@@ -318,12 +327,12 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
 // ------------------------------------------------------------------------- host launcher
 using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
-                         int64_t, const void*, int64_t, void* const*, int, int64_t, cudaStream_t);
+                         int64_t, const void*, int64_t, void* const*, int, int64_t, bool, cudaStream_t);
 
 template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
 int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N, int K,
                 const void* A, int64_t lda, const void* B, int64_t ldb, void* const* C_list, int n_dst,
-                int64_t ldc, cudaStream_t stream) {
+                int64_t ldc, bool is_bf16, cudaStream_t stream) {
     using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
     auto kernel = gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC_BUFS>;
 
@@ -377,7 +386,8 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     attr[0].val.clusterDim.z = 1;
     lc.attrs = attr;
     lc.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, n_dst, M, N, K, cfg.bs_w, dev->status);
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, n_dst, M, N, K, cfg.bs_w,
+                                       is_bf16 ? 1 : 0, dev->status);
     if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
     return B200_OK;
 }
@@ -520,7 +530,28 @@ int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t ld
         return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
                     dev->max_smem_optin);
     }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, static_cast<cudaStream_t>(stream));
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, static_cast<cudaStream_t>(stream));
+}
+
+int b200_gemm_f16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
+                      int64_t ldb, void* C, int64_t ldc, void* stream) {
+    using namespace b200;
+    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
+    const Entry& e = kEntries[config];
+    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
+    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
+    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
+    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
+        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
+                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
+    }
+    const DeviceInfo* dev = current_device();
+    if (dev == nullptr) return B200_ENODEVICE;
+    if (e.cfg.smem_bytes > dev->max_smem_optin) {
+        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
+                    dev->max_smem_optin);
+    }
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, false, static_cast<cudaStream_t>(stream));
 }
 
 int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
@@ -544,7 +575,7 @@ int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, in
         return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
                     dev->max_smem_optin);
     }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, static_cast<cudaStream_t>(stream));
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, true, static_cast<cudaStream_t>(stream));
 }
 
 int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
@@ -575,7 +606,7 @@ int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, in
     // for this launch's record.  Ordered on the caller's stream, ahead of the kernel.
     cudaError_t ce = cudaMemsetAsync(dev->status, 0, kStatusBlockBytes, static_cast<cudaStream_t>(stream));
     if (ce != cudaSuccess) return fail(B200_ECUDA, "clearing the scratch block failed: %s", cudaGetErrorString(ce));
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, static_cast<cudaStream_t>(stream));
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -69,6 +69,28 @@ def gemm_bf16_tn(a, b, out=None, config=None):
     return out
 
 
+def gemm_f16_tn(a, b, out=None, config=None):
+    """C = A @ B^T for fp16 operands and output (fp32 accumulation)."""
+    _check_matrix(a, "a", torch.float16)
+    _check_matrix(b, "b", torch.float16)
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2 or b.device != a.device:
+        raise ValueError("a [M,K] and b [N,K] must share K and the device")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=a.device)
+    else:
+        _check_matrix(out, "out", torch.float16)
+        if tuple(out.shape) != (M, N) or out.device != a.device:
+            raise ValueError("out has the wrong shape or device")
+    idx = gemm_config_index(config, M, N, K)
+    with torch.cuda.device(a.device):
+        capi.check(capi.lib().b200_gemm_f16_tn(
+            idx, M, N, K, a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+            out.data_ptr(), out.stride(0), _stream_ptr(a.device)))
+    return out
+
+
 def gemm_bf16_tn_scatter(a, b, outs, config=None):
     """C = A @ B^T written to every tensor in `outs` (1..8 [M,N] windows with one common
     leading dimension; they may alias other GPUs' memory, e.g. symmetric-memory buffers)."""

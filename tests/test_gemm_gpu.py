@@ -225,3 +225,23 @@ def test_scatter_writes_every_destination(env):
         ops.gemm_bf16_tn_scatter(a, b, [])
     ptrs = (ctypes.c_void_p * 9)(*[outs[0].data_ptr()] * 9)
     assert lib.b200_gemm_bf16_tn_scatter(0, 256, 256, 64, a.data_ptr(), 64, b.data_ptr(), 64, ptrs, 9, 256, None) == -1
+
+
+def test_fp16_operands(env):
+    """fp16 in / fp16 out through b200_gemm_f16_tn against numpy float64."""
+    torch, capi, lib, oracle, dev = env
+    from sm120_dl_b200 import ops
+    M, N, K = 512, 768, 320
+    rng = np.random.Generator(np.random.PCG64(61))
+    a_h = rng.uniform(-1, 1, size=(M, K)).astype(np.float16)
+    b_h = rng.uniform(-1, 1, size=(N, K)).astype(np.float16)
+    ref = a_h.astype(np.float64) @ b_h.astype(np.float64).T
+    a, b = torch.from_numpy(a_h).to(dev), torch.from_numpy(b_h).to(dev)
+    for cfg in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn128_bk64_s6_cta1_acc2_bsw8"):
+        c = ops.gemm_f16_tn(a, b, config=cfg)
+        assert capi.device_status() == 0
+        st = oracle.compare(c.float().cpu().numpy(), ref, 1e-2, 5e-2)
+        # fp16 output: half an ulp is 2^-11, far inside the bounded relative error of 1e-2
+        assert st["passed"] and st["max_rel_bounded"] <= 2e-3, st
+    with pytest.raises(ValueError):
+        ops.gemm_f16_tn(a.bfloat16(), b)

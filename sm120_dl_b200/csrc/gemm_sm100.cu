@@ -194,7 +194,9 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
     } else if (warp == 1) {
         // -------------------------------------------------------------------- MMA issuer
-        if (lane == 0 && is_leader) {
+        // The whole warp runs the loop and one elected lane issues: tcgen05.mma issued from
+        // warp-uniform code costs fewer issue cycles than from a single diverged lane.
+        if (is_leader) {
             // operand format: bf16 (1) or fp16 (0); the accumulator is fp32 either way
             const uint32_t idesc = make_idesc_f16(BM, BN, is_bf16 ? 1 : 0, 0, 0);
             int s = 0;
@@ -204,27 +206,31 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             for (int tile = group; tile < num_tiles && ok; tile += num_groups, ++local_tile) {
                 const uint32_t buf = local_tile % ACC_BUFS;
                 const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
-                ok = mbar_wait(guard, accempty_bar + 8 * buf, acc_ph ^ 1u, 0x200u + buf);
+                ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8 * buf, acc_ph ^ 1u, 0x200u + buf));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
                 for (int kb = 0; kb < k_blocks; ++kb) {
-                    ok = mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s);
+                    ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s));
                     if (!ok) break;
                     tc_fence_after();
                     const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + s * kAStageBytes);
                     const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + s * T::kBStageBytes);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kBK / 16; ++k) {
-                        // 16 elements of K = 32 bytes inside the swizzled row = +2 in the
-                        // descriptor's 16-byte address units.
-                        mma_ss<CTA_GROUP>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                          (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < kBK / 16; ++k) {
+                            // 16 elements of K = 32 bytes inside the swizzled row = +2 in the
+                            // descriptor's 16-byte address units.
+                            mma_ss<CTA_GROUP>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                              (kb | k) != 0 ? 1u : 0u);
+                        }
+                        mma_commit<CTA_GROUP>(empty_bar + 8 * s);
                     }
-                    mma_commit<CTA_GROUP>(empty_bar + 8 * s);
+                    __syncwarp();
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
-                if (ok) mma_commit<CTA_GROUP>(accfull_bar + 8 * buf);
+                if (ok && elect_one()) mma_commit<CTA_GROUP>(accfull_bar + 8 * buf);
+                __syncwarp();
             }
         }
     } else {

@@ -37,6 +37,11 @@ constexpr int kFaThreads = 384;
 constexpr int kBoxBytes = 128 * 128;      // one TMA box: 128 rows x 64 fp16 (128 bytes)
 constexpr int kMaxDst = 8;                // copies of O one launch can write (one per GPU of a box)
 constexpr float kRescaleLog2 = 8.0f;      // rescale O only when the max grew by > 2^8
+// P V of a block is issued in two parts, 16-key MMA steps [0, kSplitP) and [kSplitP, 8): the
+// first starts while the softmax warps still work on the last keys, so only the short
+// second part and the next S stand between two softmax passes of a tile.
+constexpr int kSplitP = 6;
+static_assert(kSplitP == 2 || kSplitP == 4 || kSplitP == 6, "parts end on 32-key chunks");
 // Register budget after the role split.  setmaxnreg.inc blocks until the CTA's own pool
 // (registers per thread at launch x threads) can supply the increase, so the two budgets
 // must fit in what the CTA was launched with or the kernel never gets past the split.
@@ -157,7 +162,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
     const uint32_t kv_full = q_full + 8;                  // [STAGES] TMA -> MMA
     const uint32_t kv_empty = kv_full + 8 * STAGES;       // [STAGES] MMA -> TMA
     const uint32_t s_full = kv_empty + 8 * STAGES;        // [2] MMA -> softmax: S_i (or final O_i) ready
-    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: half h of P_i written (and O_i rescaled)
+    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: part h of P_i written (and O_i rescaled)
     const uint32_t tmem_slot = p_full + 32;
     const uint32_t abort_slot = tmem_slot + 4;
     uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -268,13 +273,13 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                               smem_desc_kmajor_sw128(k_addr + off), idesc_qk, kk > 0 ? 1u : 0u);
                 }
             };
-            // Half h of P V: keys [64h, 64h+64) of the block.  P: 16 keys = 8 packed columns.
+            // Part h of P V: 16-key steps [0,kSplitP) or [kSplitP,8) of the block.  P: 16 keys = 8 packed columns.
             // V: 16 key rows = 2048 bytes; the second 64-wide span of the head dimension lives
             // one box (16 KiB) further.
             auto issue_pv_half = [&](int i, int h, uint32_t v_addr, bool accumulate) {
                 if (!elect_one()) return;
 #pragma unroll
-                for (int kk = 4 * h; kk < 4 * h + 4; ++kk) {
+                for (int kk = (h ? kSplitP : 0); kk < (h ? 8 : kSplitP); ++kk) {
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
                            smem_desc_mnmajor_sw128(v_addr + kk * 2048, kBoxBytes), idesc_pv,
                            (accumulate || kk > 0) ? 1u : 0u);
@@ -451,12 +456,12 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
                 // 32 keys = 16 packed columns; S is already in registers, so P may overwrite it.
                 tmem_st_32x32b_x16(t_s + c * 16, pr);
-                if (c & 1) {
-                    // Half of P is in tensor memory: let the MMA warp start on it.
+                if (c == kSplitP / 2 - 1 || c == 3) {
+                    // The first part (or all) of P is in tensor memory: let the MMA warp start on it.
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(p_full + 16 * i + 8 * (c >> 1));
+                    if (lane == 0) mbar_arrive(p_full + 16 * i + 8 * (c == 3 ? 1 : 0));
                 }
             }
             unpack2(add2(add2(lsum[0], lsum[1]), add2(lsum[2], lsum[3])), l0, l1);

@@ -83,6 +83,7 @@ def build_lib(force=False, verbose=False, ptxas_verbose=False):
             if verbose:
                 print(" ".join(cmd), flush=True)
             procs.append((cmd, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
+    report = []
     for cmd, p in procs:
         out, _ = p.communicate()
         if p.returncode != 0:
@@ -90,6 +91,11 @@ def build_lib(force=False, verbose=False, ptxas_verbose=False):
             raise RuntimeError(f"build step failed: {' '.join(cmd)}")
         if ptxas_verbose:
             print(out)
+            report.append(out)
+    if ptxas_verbose and report:
+        # input of flashattention/extract_resources.py
+        with open(os.path.join(HERE, "build", "build.log"), "w") as f:
+            f.write("\n".join(report))
     if force or procs or _newer(objs, LIB):
         tmp = LIB + ".tmp"
         _run([NVCC] + ARCH_FLAGS + ["-ccbin", HOST_CXX, "-shared", "-o", tmp] + objs + ["-lcudart"], verbose)

@@ -223,3 +223,28 @@ def test_gather_logic_two_ranks_gloo(tmp_path):
     for rank, p in enumerate(procs):
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0 and f"rank {rank} ok" in out, out[-2000:]
+
+
+def test_extract_resources_maps_kernels_to_config_names(tmp_path):
+    """The ptxas report parser names kernels like the registries do (reference tool:
+    flashattention/v3_mMnNkN/extract_resources.py)."""
+    import importlib.util
+    path = os.path.join(ROOT, "sm120_dl_b200", "flashattention", "extract_resources.py")
+    spec = importlib.util.spec_from_file_location("extract_resources", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    log = tmp_path / "build.log"
+    log.write_text(
+        "ptxas info    : Compiling entry function '_ZN4b2003_GLOBAL__N_13fa_fwd_kernelILi128ELi5ELi0EEEvPj' for 'sm_100a'\n"
+        "ptxas info    : Function properties for x\n"
+        "    8 bytes stack frame, 4 bytes spill stores, 12 bytes spill loads\n"
+        "ptxas info    : Used 168 registers, used 16 barriers\n"
+        "ptxas info    : Compiling entry function '_ZN4b20019gemm_bf16_tn_kernelILi256ELi6ELi2ELi2EEEvi' for 'sm_100a'\n"
+        "    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads\n"
+        "ptxas info    : Used 96 registers\n")
+    out = tmp_path / "resource.log"
+    assert mod.main([str(log), str(out)]) == 0
+    lines = out.read_text().splitlines()
+    assert lines[0] == "func_name spill stack registers"
+    assert lines[1] == "hd128_bm64_bn64_tq128x2_tk128_s5_e0 16 8 168"
+    assert lines[2] == "bf16_bm256_bn256_bk64_s6_cta2_acc2 0 0 96"

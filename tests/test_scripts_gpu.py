@@ -49,3 +49,15 @@ def test_compute_rate_script_lists_and_runs(built):
     name = [n for n in p.stdout.split() if n.startswith("hd64_")][0]
     p = _py("test_compute_rate.py", "--func", name, "--seq-len", "512", "--head-num", "4", "--batch", "1", "--sleep", "0")
     assert p.returncode == 0 and "PROFILE func=" in p.stdout and "DONE func=" in p.stdout
+
+
+def test_single_case_runner(built):
+    p = _py("test.py")
+    assert p.returncode == 0 and " hd=128 bm=64 bn=64 " in p.stdout
+    name = [line.split()[0] for line in p.stdout.splitlines() if line.startswith("hd128_")][0]
+    p = _py("test.py", "--config", "b2_hn4_seq512_hd128_casual1", "--func", name)
+    assert p.returncode == 0, p.stdout + p.stderr
+    assert p.stdout.startswith(f"RUN b2_hn4_seq512_hd128_casual1 func={name}")
+    assert "DONE b2_hn4_seq512_hd128_casual1" in p.stdout and "output_shape=(2, 512, 4, 128)" in p.stdout
+    p = _py("test.py", "--config", "512", "64", "4", "2", "0", "--func", name)
+    assert p.returncode != 0 and "expects head_dim=128, got 64" in p.stderr

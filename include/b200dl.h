@@ -47,6 +47,9 @@ typedef struct b200_gemm_config {
     int bs_w;           /* raster: N-tiles per strip, M-major inside a strip                 */
     int smem_bytes;     /* dynamic shared memory per CTA                                     */
     int tmem_cols;      /* tensor-memory columns allocated per CTA                           */
+    int split_k;        /* 1, or the cluster size of a split-K config: that many CTAs share one
+                           output tile, each accumulating its share of K; the partial tiles are
+                           summed through distributed shared memory (no workspace)           */
 } b200_gemm_config;
 
 int b200_gemm_num_configs(void);
@@ -54,9 +57,10 @@ int b200_gemm_num_configs(void);
 const b200_gemm_config* b200_gemm_get_config(int idx);
 /* Index of the config with exactly this name, or -1. */
 int b200_gemm_find_config(const char* name);
-/* Index of the config this library would pick for the shape (largest tile that still
- * fills the GPU, discounted by the work wasted on ragged edges), or -1 for a non-positive
- * shape. */
+/* Index of the config this library would pick for the shape, or -1 for a non-positive
+ * shape: the cheapest under a cost model of waves x k-blocks per CTA x tile width over the
+ * measured efficiency of that MMA width.  Split-K configs are candidates only when the
+ * tiles alone number fewer than 148 and every CTA of the cluster keeps >= 16 k-blocks. */
 int b200_gemm_default_config(int M, int N, int K);
 
 /* C[M,N] = A[M,K] * B[N,K]^T, bf16 operands, fp32 accumulation, bf16 round-to-nearest-even

@@ -23,7 +23,7 @@ class GemmConfig(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("bm", ctypes.c_int), ("bn", ctypes.c_int),
                 ("bk", ctypes.c_int), ("stages", ctypes.c_int), ("cta_group", ctypes.c_int),
                 ("acc_bufs", ctypes.c_int), ("bs_w", ctypes.c_int), ("smem_bytes", ctypes.c_int),
-                ("tmem_cols", ctypes.c_int)]
+                ("tmem_cols", ctypes.c_int), ("split_k", ctypes.c_int)]
 
 
 class FaConfig(ctypes.Structure):

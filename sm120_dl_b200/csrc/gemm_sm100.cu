@@ -331,6 +331,199 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
 }
 
+// ------------------------------------------------------------------------- split-K kernel
+// For shapes with too few output tiles to occupy the GPU (M = 128 with a long K: the problem
+// is then bound by reading B once from HBM, and only CTAs that are loading count).  A cluster
+// of SPLIT CTAs shares one 128 x BN output tile: CTA r accumulates k-blocks
+// [r*kb/SPLIT, (r+1)*kb/SPLIT) in tensor memory, parks its fp32 partial tile in its own shared
+// memory (over the drained ring), and after a cluster barrier each CTA sums a 128/SPLIT-row
+// band of all partials through distributed shared memory, in rank order (deterministic),
+// rounds once and stores to C.  No workspace in global memory, no second kernel.
+struct CPtrSet {
+    void* p[kMaxDst];
+};
+
+template <int BN, int STAGES>
+struct SplitKTraits {
+    static constexpr int kBStageBytes = BN * 128;
+    static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+    static constexpr int kRingBytes = STAGES * kStageBytes;
+    static constexpr int kPartialBytes = kCtaM * BN * 4;   // [BN/4][128 rows][4 floats]
+    static constexpr int kBarrierBytes = (2 * STAGES + 1) * 8 + 16;
+    static constexpr int kSmemBytes = kRingBytes + kBarrierBytes + 1024;
+    static constexpr int kTmemCols = tmem_cols_for(BN);
+    static_assert(BN == 64 || BN == 128, "split-K tiles are 128 x 64 or 128 x 128");
+    static_assert(kPartialBytes <= kRingBytes, "the partial tile must fit over the ring");
+    static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB shared-memory limit of sm_100");
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const __grid_constant__ CPtrSet c_list, int n_dst, int64_t ldc, int M, int N, int K,
+                   int split, int is_bf16, uint32_t* status) {
+    using T = SplitKTraits<BN, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t ring_a = smem_base;
+    const uint32_t ring_b = smem_base + STAGES * kAStageBytes;
+    const uint32_t partial = smem_base;                       // over the ring, after the mainloop
+    const uint32_t bar_base = smem_base + T::kRingBytes;
+    const uint32_t full_bar = bar_base;                       // [STAGES] TMA -> MMA
+    const uint32_t empty_bar = full_bar + STAGES * 8;         // [STAGES] MMA -> TMA
+    const uint32_t accfull_bar = empty_bar + STAGES * 8;      // MMA -> epilogue
+    const uint32_t tmem_slot = accfull_bar + 8;
+    const uint32_t abort_slot = tmem_slot + 4;
+    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
+    volatile uint32_t* abort_ptr = reinterpret_cast<volatile uint32_t*>(smem_aligned + (abort_slot - smem_base));
+    const WaitGuard guard{abort_ptr, status};
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(cluster_ctarank());     // = blockIdx.x % split
+    const int tile = static_cast<int>(blockIdx.x) / split;
+    const int tiles_n = (N + BN - 1) / BN;
+    const int tm = tile / tiles_n, tn = tile - tm * tiles_n;
+    // k-blocks of this rank: an even share, the first (total % split) ranks take one more
+    const int kb_total = (K + kBK - 1) / kBK;
+    const int kb_base = kb_total / split, kb_rem = kb_total - kb_base * split;
+    const int kb_begin = rank * kb_base + min(rank, kb_rem);
+    const int kb_count = kb_base + (rank < kb_rem ? 1 : 0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(full_bar + 8 * s, 1);
+            mbar_init(empty_bar + 8 * s, 1);
+        }
+        mbar_init(accfull_bar, 1);
+        *abort_ptr = 0;
+        fence_mbar_init();
+        prefetch_tensormap(&tmap_a);
+        prefetch_tensormap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc<1>(tmem_slot, T::kTmemCols);
+        tmem_relinquish<1>();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int kb = 0; kb < kb_count; ++kb) {
+                if (!mbar_wait(guard, empty_bar + 8 * s, ph ^ 1u, 0x2100u + s)) break;
+                mbar_arrive_expect_tx(full_bar + 8 * s, T::kStageBytes);
+                tma_load_2d(ring_a + s * kAStageBytes, &tmap_a, full_bar + 8 * s, (kb_begin + kb) * kBK, tm * kCtaM);
+                tma_load_2d(ring_b + s * T::kBStageBytes, &tmap_b, full_bar + 8 * s, (kb_begin + kb) * kBK, tn * BN);
+                if (++s == STAGES) { s = 0; ph ^= 1u; }
+            }
+        }
+    } else if (warp == 1) {
+        const uint32_t idesc = make_idesc_f16(kCtaM, BN, is_bf16 ? 1 : 0, 0, 0);
+        int s = 0;
+        uint32_t ph = 0;
+        bool ok = true;
+        for (int kb = 0; kb < kb_count; ++kb) {
+            ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x2300u + s));
+            if (!ok) break;
+            tc_fence_after();
+            const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + s * kAStageBytes);
+            const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + s * T::kBStageBytes);
+            if (elect_one()) {
+#pragma unroll
+                for (int k = 0; k < kBK / 16; ++k)
+                    mma_ss<1>(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                mma_commit<1>(empty_bar + 8 * s);
+            }
+            __syncwarp();
+            if (++s == STAGES) { s = 0; ph ^= 1u; }
+        }
+        if (ok && kb_count > 0 && elect_one()) mma_commit<1>(accfull_bar);
+        __syncwarp();
+    } else {
+        // park the fp32 partial tile: thread = row, 4 columns per 16-byte store, column-group major
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        bool ok = true;
+        if (kb_count > 0) {
+            ok = __all_sync(0xffffffffu, mbar_wait(guard, accfull_bar, 0, 0x2400u));
+            tc_fence_after();
+        }
+        if (ok) {
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t acc[32];
+                if (kb_count > 0) {
+                    tmem_ld_32x32b_x32(t_row + c * 32, acc);
+                    tmem_wait_ld();
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) acc[x] = 0u;
+                }
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    st_shared_v4(partial + (c * 8 + g) * (kCtaM * 16) + row * 16, acc[4 * g], acc[4 * g + 1],
+                                 acc[4 * g + 2], acc[4 * g + 3]);
+            }
+        }
+    }
+
+    // every partial of the cluster is in place
+    tc_fence_before();
+    __syncwarp();
+    cluster_arrive();
+    cluster_wait();
+
+    if (warp >= 2 && *abort_ptr == 0) {
+        const int rows_per = kCtaM / split;
+        const int t = threadIdx.x - 64;
+        for (int idx = t; idx < rows_per * (BN / 4); idx += kEpiWarps * 32) {
+            const int cg = idx / rows_per;
+            const int row = rank * rows_per + (idx - cg * rows_per);
+            const uint32_t local = partial + cg * (kCtaM * 16) + row * 16;
+            float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+            for (int r = 0; r < split; ++r) {
+                float a, b, c, d;
+                ld_shared_cluster_v4(mapa_cluster(local, static_cast<uint32_t>(r)), a, b, c, d);
+                s0 += a; s1 += b; s2 += c; s3 += d;
+            }
+            const int grow = tm * kCtaM + row, gcol = tn * BN + cg * 4;
+            if (grow < M && gcol < N) {
+                uint2 out;
+                if (is_bf16) {
+                    __nv_bfloat162 v0 = __floats2bfloat162_rn(s0, s1), v1 = __floats2bfloat162_rn(s2, s3);
+                    out.x = *reinterpret_cast<uint32_t*>(&v0);
+                    out.y = *reinterpret_cast<uint32_t*>(&v1);
+                } else {
+                    __half2 v0 = __floats2half2_rn(s0, s1), v1 = __floats2half2_rn(s2, s3);
+                    out.x = *reinterpret_cast<uint32_t*>(&v0);
+                    out.y = *reinterpret_cast<uint32_t*>(&v1);
+                }
+                for (int d = 0; d < n_dst; ++d)
+                    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(c_list.p[d]) + static_cast<int64_t>(grow) * ldc + gcol) = out;
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------- teardown
+    if (*abort_ptr != 0) {
+        for (int i = 0; i < 64; ++i) __nanosleep(100000);
+    }
+    // no CTA may exit (and release its shared memory) while a peer still reads its partial
+    cluster_arrive();
+    cluster_wait();
+    if (warp == 1) {
+        __syncwarp();
+        tmem_dealloc<1>(tmem_base, T::kTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------------- host launcher
 using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
                          int64_t, const void*, int64_t, void* const*, int, int64_t, bool, cudaStream_t);
@@ -398,6 +591,65 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     return B200_OK;
 }
 
+template <int BN, int STAGES>
+int launch_gemm_splitk(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N, int K, const void* A,
+                       int64_t lda, const void* B, int64_t ldb, void* const* C_list, int n_dst, int64_t ldc,
+                       bool is_bf16, cudaStream_t stream) {
+    using T = SplitKTraits<BN, STAGES>;
+    auto kernel = gemm_splitk_kernel<BN, STAGES>;
+    const int split = cfg.split_k;
+    if ((K + kBK - 1) / kBK < split)
+        return fail(B200_ESHAPE, "%s: K=%d has fewer 64-element blocks than the %d-way split", cfg.name, K, split);
+
+    CUtensorMap tmap_a, tmap_b;
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(M)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(lda) * 2};
+        const uint32_t box[2] = {kBK, kCtaM};
+        if (int rc = encode_tmap_2byte(&tmap_a, A, 2, dims, strides, box, true)) return rc;
+    }
+    {
+        const uint64_t dims[2] = {static_cast<uint64_t>(K), static_cast<uint64_t>(N)};
+        const uint64_t strides[1] = {static_cast<uint64_t>(ldb) * 2};
+        const uint32_t box[2] = {kBK, static_cast<uint32_t>(BN)};
+        if (int rc = encode_tmap_2byte(&tmap_b, B, 2, dims, strides, box, true)) return rc;
+    }
+    CPtrSet c_list;
+    std::memset(&c_list, 0, sizeof(c_list));
+    for (int d = 0; d < n_dst; ++d) {
+        if ((reinterpret_cast<uintptr_t>(C_list[d]) & 7u) != 0)
+            return fail(B200_EINVAL, "%s: C must be 8-byte aligned", cfg.name);
+        c_list.p[d] = C_list[d];
+    }
+
+    static bool attr_done[64] = {};
+    if (!attr_done[dev->device]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
+        if (e != cudaSuccess) return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", cfg.name,
+                                          T::kSmemBytes, cudaGetErrorString(e));
+        attr_done[dev->device] = true;
+    }
+    const long tiles = static_cast<long>((M + kCtaM - 1) / kCtaM) * ((N + BN - 1) / BN);
+    if (tiles * split > 0x7fffffffL) return fail(B200_ESHAPE, "%s: too many tiles", cfg.name);
+
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(tiles * split), 1, 1);
+    lc.blockDim = dim3(kThreads, 1, 1);
+    lc.dynamicSmemBytes = T::kSmemBytes;
+    lc.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(split);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, c_list, n_dst, ldc, M, N, K, split,
+                                       is_bf16 ? 1 : 0, dev->status);
+    if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
+    return B200_OK;
+}
+
 struct Entry {
     b200_gemm_config cfg;
     LaunchFn launch;
@@ -406,13 +658,18 @@ struct Entry {
 #define B200_GEMM_CONFIG(NAME, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)                                  \
     Entry{b200_gemm_config{NAME, kCtaM * CTA_GROUP, BN, kBK, STAGES, CTA_GROUP, ACC_BUFS, BS_W,        \
                            GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kSmemBytes,                    \
-                           GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kTmemCols},                    \
+                           GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kTmemCols, 1},                 \
           &launch_gemm<BN, STAGES, CTA_GROUP, ACC_BUFS>},
+#define B200_GEMM_SPLITK_CONFIG(NAME, BN, STAGES, SPLIT_K)                                             \
+    Entry{b200_gemm_config{NAME, kCtaM, BN, kBK, STAGES, 1, 1, 1, SplitKTraits<BN, STAGES>::kSmemBytes, \
+                           SplitKTraits<BN, STAGES>::kTmemCols, SPLIT_K},                              \
+          &launch_gemm_splitk<BN, STAGES>},
 
 const Entry kEntries[] = {
 #include "generated/gemm_configs.inc"
 };
 #undef B200_GEMM_CONFIG
+#undef B200_GEMM_SPLITK_CONFIG
 
 constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
 
@@ -491,27 +748,34 @@ int b200_gemm_find_config(const char* name) {
 }
 
 int b200_gemm_default_config(int M, int N, int K) {
-    // Prefer the config with the largest tile area whose tile count still covers every SM
-    // pair at least once; fall back to the legal config with the most tiles.
+    // Cost model in units of "one k-block of a 128 x 256 CTA tile at full tensor rate":
+    //   waves of CTA groups over the 148 SMs  x  k-blocks per CTA  x  tile width / efficiency
+    // with the measured efficiency of each MMA width (a 128 x N x 16 MMA costs >= ~74 cycles
+    // whatever N is: 8192^3 runs at 1.55 / 1.11 / 0.67 PFLOP/s with N = 256 / 128 / 64), plus a per-tile epilogue and, for split-K, the cluster reduction.  Work on
+    // a ragged edge is paid like any other, so oversized tiles lose by themselves.
+    if (M <= 0 || N <= 0 || K <= 0) return -1;
     int best = -1;
-    long best_score = -1;
+    double best_cost = 0.0;
     for (int i = 0; i < b200::kNumEntries; ++i) {
         const b200_gemm_config& c = b200::kEntries[i].cfg;
-        if (M <= 0 || N <= 0 || K <= 0) continue;
         const long tiles = static_cast<long>((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
-        // work wasted on the ragged edge counts against a large tile
-        const double useful = static_cast<double>(M) * N / (static_cast<double>(tiles) * c.bm * c.bn);
-        const long ctas = tiles * c.cta_group;
-        const long area = static_cast<long>(static_cast<double>(c.bm) * c.bn * useful);
-        // Enough tiles to occupy 148 SMs: largest tile, then deepest ring, strip width 8
-        // (fastest measured on 8192^3).  Otherwise: most SMs busy, single-CTA MMA first
-        // (no pair synchronisation to pay for on a latency-bound problem), then larger tile.
-        const long score = (ctas >= 148)
-                               ? (1000000000L + area * 64 + c.stages * 4 + (c.bs_w == 8 ? 2 : 0) + c.cta_group)
-                               : (static_cast<long>(ctas * useful * 1000.0) * 1000L + (c.cta_group == 1 ? 500L : 0L) +
-                                  area / 1024 + c.stages);
-        if (score > best_score) {
-            best_score = score;
+        const long kb = (K + c.bk - 1) / c.bk;
+        if (c.split_k > 1 && (tiles >= 148 || kb / c.split_k < 16)) continue;  // see b200dl.h
+        const long groups = tiles * c.split_k;                // CTA pairs, CTAs or split-K CTAs
+        const long slots = 148 / c.cta_group;
+        const long waves = (groups + slots - 1) / slots;
+        // the CTA pair halves each CTA's B traffic but pays a pair handshake per tile: worth it
+        // only on a full GPU
+        const double eff = (c.bn >= 256 ? 1.0 : c.bn >= 192 ? 0.90 : c.bn >= 128 ? 0.72 : 0.43) *
+                           (c.cta_group == 2 ? (tiles >= 74 ? 1.03 : 0.99) : 1.0);
+        const double kb_per_cta = static_cast<double>((kb + c.split_k - 1) / c.split_k);
+        // persistent kernels overlap all but the last epilogue with the next tile's mainloop
+        const double epilogue = c.split_k > 1 ? waves * (8.0 + 2.0 * c.split_k) : (c.acc_bufs > 1 ? 4.0 : 4.0 * waves);
+        double cost = waves * kb_per_cta * (c.bn / 256.0) / eff + epilogue;
+        // ties: deeper ring, strip width 8 (fastest measured on 8192^3)
+        cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == 8 ? 0.0002 : 0.0);
+        if (best < 0 || cost < best_cost) {
+            best_cost = cost;
             best = i;
         }
     }

@@ -376,6 +376,14 @@ __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 16-byte load from the shared memory of any CTA of the cluster (address from mapa_cluster).
+__device__ __forceinline__ void ld_shared_cluster_v4(uint32_t cluster_addr, float& a, float& b, float& c,
+                                                     float& d) {
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(a), "=f"(b), "=f"(c), "=f"(d)
+                 : "r"(cluster_addr)
+                 : "memory");
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
                                              uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),

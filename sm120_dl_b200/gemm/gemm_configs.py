@@ -13,6 +13,10 @@ vocabulary is Blackwell's: instead of warp grids for mma.sync it chooses
               mainloop of tile i+1
   bs_w        raster strip width in N-tiles (same idea as block_swizzle<BS_W>,
               utils/tools.h:30-40)
+  split_k     split-K configs (for shapes with too few tiles to occupy the GPU, e.g. M = 128
+              with a long K): a cluster of split_k CTAs shares one 128 x bn tile, each CTA
+              accumulates its share of K and the partial tiles are summed through
+              distributed shared memory
 
 Legality is decided by the hardware budgets of one SM: 227 KiB of shared memory, 512
 tensor-memory columns, tcgen05.mma shape rules.  Two files are written: a C include with
@@ -111,6 +115,35 @@ def generate_configs(max_smem_kb, full=False):
     return configs
 
 
+SPLITK_BN_VALUES = (64, 128)
+SPLITK_VALUES = (2, 4, 8)          # cluster sizes; 8 is the portable maximum
+
+
+def splitk_smem_bytes(bn, stages):
+    barrier_bytes = (2 * stages + 1) * 8 + 16
+    return stages * stage_bytes(bn, 1) + barrier_bytes + ALIGN_SLACK
+
+
+def splitk_config_name(bn, stages, split_k):
+    return f"bf16_bm{CTA_M}_bn{bn}_bk{BK}_s{stages}_cta1_splitk{split_k}"
+
+
+def generate_splitk_configs(max_smem_kb):
+    """Returns a list of (name, bn, stages, split_k): per tile width the deepest ring that
+    fits (the fp32 partial tile, 128 x bn x 4 bytes, reuses the drained ring)."""
+    max_smem = max_smem_kb * 1024
+    configs = []
+    for bn in SPLITK_BN_VALUES:
+        legal = [s for s in STAGE_VALUES
+                 if splitk_smem_bytes(bn, s) <= max_smem and s * stage_bytes(bn, 1) >= CTA_M * bn * 4]
+        if not legal:
+            continue
+        stages = legal[-1]
+        for split_k in SPLITK_VALUES:
+            configs.append((splitk_config_name(bn, stages, split_k), bn, stages, split_k))
+    return configs
+
+
 class _write_if_changed:
     """open(path, "w") that leaves the file (and its mtime) alone when the content is
     unchanged, so a rebuild is triggered only by a real change of the config list."""
@@ -138,17 +171,20 @@ class _write_if_changed:
         return False
 
 
-def write_inc(path, configs, max_smem_kb):
+def write_inc(path, configs, max_smem_kb, splitk=()):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
     with _write_if_changed(path) as f:
         f.write("// Auto-generated by gemm_configs.py - do not edit\n")
-        f.write(f"// {len(configs)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
+        f.write(f"// {len(configs) + len(splitk)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
         f.write("// B200_GEMM_CONFIG(name, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)\n")
         for name, bn, stages, cta_group, acc_bufs, bs_w in configs:
             f.write(f'B200_GEMM_CONFIG("{name}", {bn}, {stages}, {cta_group}, {acc_bufs}, {bs_w})\n')
+        f.write("// B200_GEMM_SPLITK_CONFIG(name, BN, STAGES, SPLIT_K)\n")
+        for name, bn, stages, split_k in splitk:
+            f.write(f'B200_GEMM_SPLITK_CONFIG("{name}", {bn}, {stages}, {split_k})\n')
 
 
-def write_registry(path, configs):
+def write_registry(path, configs, splitk=()):
     """Entries of kGemmConfigs[] for gemm_config_registry.cpp: one line per config, the
     index being the config's position in libb200dl.so's own table."""
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
@@ -158,6 +194,8 @@ def write_registry(path, configs):
         for i, (name, bn, stages, cta_group, acc_bufs, bs_w) in enumerate(configs):
             f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M * cta_group}, {bn}, {BK}, {stages}, '
                     f'{cta_group}, {acc_bufs}, {bs_w})\n')
+        for i, (name, bn, stages, split_k) in enumerate(splitk, start=len(configs)):
+            f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M}, {bn}, {BK}, {stages}, 1, 1, 1)\n')
 
 
 def write_cmake(path, configs, max_smem_kb):
@@ -197,11 +235,12 @@ def main(argv=None):
     configs = generate_configs(args.max_smem_kb, full=args.full)
     if not configs:
         raise RuntimeError("no valid GEMM configs generated")
-    write_inc(args.inc, configs, args.max_smem_kb)
-    write_registry(args.registry, configs)
+    splitk = generate_splitk_configs(args.max_smem_kb)
+    write_inc(args.inc, configs, args.max_smem_kb, splitk)
+    write_registry(args.registry, configs, splitk)
     if args.output:
         write_cmake(args.output, configs, args.max_smem_kb)
-    print(f"Generated {len(configs)} configs -> {os.path.normpath(args.inc)}")
+    print(f"Generated {len(configs)} + {len(splitk)} split-K configs -> {os.path.normpath(args.inc)}")
     return configs
 
 

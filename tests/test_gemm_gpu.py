@@ -66,8 +66,10 @@ def test_every_config_on_its_smallest_shapes(env, kblocks):
     """One tile and 2x3 tiles per config, with K from one k-block up (ring wrap-around)."""
     torch, capi, lib, oracle, dev = env
     for i, cfg in enumerate(capi.gemm_configs()):
-        if cfg["bs_w"] != 8 and kblocks != 2:
+        if cfg["split_k"] == 1 and cfg["bs_w"] != 8 and kblocks != 2:
             continue  # raster width changes tile order only; cover it once
+        if kblocks < cfg["split_k"]:
+            continue  # refused: fewer k-blocks than CTAs sharing the tile (tested below)
         for tm, tn in ((1, 1), (2, 3)):
             M, N, K = cfg["bm"] * tm, cfg["bn"] * tn, 64 * kblocks
             a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 100 + i, "uniform01")
@@ -245,3 +247,54 @@ def test_fp16_operands(env):
         assert st["passed"] and st["max_rel_bounded"] <= 2e-3, st
     with pytest.raises(ValueError):
         ops.gemm_f16_tn(a.bfloat16(), b)
+
+
+def test_split_k_skinny_shape_and_refusals(env):
+    """M=128 with a long K (a shape of the reference's list, gemm/test.cpp:38-61): the default
+    choice is a split-K config, every split-K config matches the fp64 oracle, runs are
+    bit-reproducible, and a K with fewer k-blocks than the split is refused."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = 128, 4096, 14336
+    cfgs = capi.gemm_configs()
+    assert cfgs[lib.b200_gemm_default_config(M, N, K)]["split_k"] > 1
+    assert cfgs[lib.b200_gemm_default_config(8192, 8192, 8192)]["split_k"] == 1
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 21)
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    ran = 0
+    for i, cfg in enumerate(cfgs):
+        if cfg["split_k"] == 1:
+            continue
+        c1 = _run(env, i, a, b, M, N, K)
+        c2 = _run(env, i, a, b, M, N, K)
+        assert torch.equal(c1.view(torch.int16), c2.view(torch.int16)), cfg["name"]
+        _check(oracle, c1.float().cpu().numpy(), ref)
+        ran += 1
+        # 3 k-blocks cannot be shared by 4 or 8 CTAs
+        if cfg["split_k"] > 3:
+            out = torch.empty((M, 64), dtype=torch.bfloat16, device=dev)
+            rc = lib.b200_gemm_bf16_tn(i, M, 64, 192, a.data_ptr(), K, b.data_ptr(), K, out.data_ptr(), 64, None)
+            assert rc == -2 and b"fewer 64-element blocks" in lib.b200_last_error()
+    assert ran == 6
+
+
+def test_split_k_ragged_shape_fp16_and_two_destinations(env):
+    """Split-K on a shape no tile divides, in fp16, and stored to two outputs at once."""
+    torch, capi, lib, oracle, dev = env
+    from sm120_dl_b200 import ops
+    M, N, K = 100, 200, 1096 + 8
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 22)
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    for name in ("bf16_bm128_bn64_bk64_s8_cta1_splitk4", "bf16_bm128_bn128_bk64_s6_cta1_splitk8"):
+        outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ops.gemm_bf16_tn_scatter(a, b, outs, config=name)
+        torch.cuda.synchronize()
+        assert capi.device_status() == 0
+        assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+        _check(oracle, outs[0].float().cpu().numpy(), ref)
+        ah, bh = a.float().half(), b.float().half()
+        ch = ops.gemm_f16_tn(ah, bh, config=name)
+        torch.cuda.synchronize()
+        want = (ah.double() @ bh.double().T)
+        assert (ch.double() - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())

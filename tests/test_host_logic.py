@@ -56,8 +56,14 @@ def test_gemm_generator_writes_reference_style_cmake(tmp_path):
     text = out.read_text()
     assert "set(GEMM_TN_MAX_SMEM_BYTES 204800)" in text and "set(GEMM_TN_CONFIGS" in text
     assert "set(GEMM_TN_DEFAULT_CONFIG" in text
+    splitk = g.generate_splitk_configs(200)
     assert inc.read_text().count("B200_GEMM_CONFIG(\"") == len(cfgs)
-    assert reg.read_text().count("B200_GEMM_ENTRY(") == len(cfgs) + 1  # + the comment line
+    assert inc.read_text().count("B200_GEMM_SPLITK_CONFIG(\"") == len(splitk) == 6
+    assert reg.read_text().count("B200_GEMM_ENTRY(") == len(cfgs) + len(splitk) + 1  # + the comment line
+    for name, bn, stages, split_k in splitk:
+        assert name == g.splitk_config_name(bn, stages, split_k) and split_k in (2, 4, 8)
+        assert g.splitk_smem_bytes(bn, stages) <= 200 * 1024
+        assert stages * g.stage_bytes(bn, 1) >= 128 * bn * 4   # the fp32 partial tile reuses the ring
 
 
 def test_flash_generator_rules(monkeypatch, tmp_path):
@@ -97,9 +103,13 @@ def test_config_tables_match_generators(lib):
     g = _import_from(os.path.join(PKG, "gemm"), "gemm_configs")
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     gc = capi.gemm_configs()
-    assert [c["name"] for c in gc] == [c[0] for c in g.generate_configs(227)]
+    assert [c["name"] for c in gc] == [c[0] for c in g.generate_configs(227) + g.generate_splitk_configs(227)]
     for c in gc:
-        assert c["smem_bytes"] == g.smem_bytes(c["bn"], c["stages"], c["cta_group"], c["acc_bufs"])
+        if c["split_k"] > 1:
+            assert c["smem_bytes"] == g.splitk_smem_bytes(c["bn"], c["stages"])
+            assert c["name"].endswith("_splitk%d" % c["split_k"]) and c["cta_group"] == 1
+        else:
+            assert c["smem_bytes"] == g.smem_bytes(c["bn"], c["stages"], c["cta_group"], c["acc_bufs"])
         assert c["tmem_cols"] == g.tmem_columns(c["bn"], c["acc_bufs"])
         assert c["bm"] == 128 * c["cta_group"] and c["bk"] == 64
     fc = capi.fa_configs()

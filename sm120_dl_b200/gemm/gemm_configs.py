@@ -195,7 +195,9 @@ def write_registry(path, configs, splitk=()):
             f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M * cta_group}, {bn}, {BK}, {stages}, '
                     f'{cta_group}, {acc_bufs}, {bs_w})\n')
         for i, (name, bn, stages, split_k) in enumerate(splitk, start=len(configs)):
-            f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M}, {bn}, {BK}, {stages}, 1, 1, 1)\n')
+            # bk = 64 * split_k: "K divisible by bk" is how the harness decides run vs skipped,
+            # and a split-K config needs at least one k-block per CTA of its cluster
+            f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M}, {bn}, {BK * split_k}, {stages}, 1, 1, 1)\n')
 
 
 def write_cmake(path, configs, max_smem_kb):

@@ -12,6 +12,10 @@ Workloads (all synthetic, seeded; shapes from the benchmark configurations):
   fa_d128             FP16 attention forward B4 H32 S4096 D128, seed 2 (heads split by rank:
                       each rank owns one such problem).
   fa_d64              FP16 attention forward B16 H32 S2048 D64, seed 3.
+  gemm_skinny         BF16 GEMM 128 x 4096 x 14336 (a shape of the reference's list), which the
+                      default config runs as cluster split-K: HBM-bound, reported against the
+                      measured copy bandwidth; five copies of B are rotated so that no step
+                      finds its 117 MB in L2.
 
 Timing: W >= 3 untimed steps, then exactly K steps between two CUDA events on the launch
 stream, bracketed by barrier + synchronize; the maximum over ranks is used.  Inputs
@@ -43,6 +47,10 @@ if ROOT not in sys.path:
 WORKLOADS = {
     "gemm8192": {"kind": "gemm", "M": 8192, "N": 8192, "K": 8192, "seed": 1,
                  "desc": "bf16 gemm M=N=K=8192, N(0,1)/sqrt(K), seed 1"},
+    # HBM-bound: B (117 MB) is read once; five copies of B are rotated so that a step never
+    # finds its B in the 126 MB L2.
+    "gemm_skinny": {"kind": "gemm", "M": 128, "N": 4096, "K": 14336, "seed": 4, "bound": "hbm", "rotate": 5,
+                    "desc": "bf16 gemm M=128 N=4096 K=14336 (split-K), N(0,1)/sqrt(K), seed 4"},
     "fa_d128": {"kind": "fa", "B": 4, "H": 32, "S": 4096, "D": 128, "seed": 2,
                 "desc": "fp16 attention fwd B4 H32 S4096 D128 non-causal, N(0,1), seed 2"},
     "fa_d64": {"kind": "fa", "B": 16, "H": 32, "S": 2048, "D": 64, "seed": 3,
@@ -52,7 +60,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
 # under profiles/ (null until a capture of that kernel exists).  fa_d128: the capture is the
 # batch-1 slice of the workload (116.1 MB); traffic grows with the batch, so x4.
-DRAM_TRAFFIC_BYTES = {"gemm8192": 1.224e9, "fa_d128": 4 * 116.1e6, "fa_d64": None}
+DRAM_TRAFFIC_BYTES = {"gemm8192": 1.224e9, "fa_d128": 4 * 116.1e6, "fa_d64": None, "gemm_skinny": None}
 
 
 def flops_per_step(w):
@@ -134,7 +142,7 @@ def cpu_sample(wname, inputs, scale=1.0):
     from oracle import oracle
     w = WORKLOADS[wname]
     if w["kind"] == "gemm":
-        rows = max(256, int(2048 * scale) // 64 * 64)
+        rows = min(w["M"], max(256, int(2048 * scale) // 64 * 64))
         a_bits, b_bits = inputs
         t0 = time.perf_counter()
         oracle.gemm_f64(a_bits, b_bits, row_begin=0, row_count=rows)
@@ -233,8 +241,16 @@ def run_gpu(args):
         cfg = ops.gemm_config_index(None, w["M"], w["N"], w["K"])
         cfg_name = capi.gemm_configs()[cfg]["name"]
 
+        # rotated copies of B for workloads smaller than L2 (kernel-only timing)
+        b_copies = [dev_in[1]] + [dev_in[1].clone() for _ in range(w.get("rotate", 1) - 1)]
+        turn = [0]
+
         def step(tensors):
-            ops.gemm_bf16_tn(tensors[0], tensors[1], out=out, config=cfg)
+            b = tensors[1]
+            if tensors is dev_in:
+                b = b_copies[turn[0] % len(b_copies)]
+                turn[0] += 1
+            ops.gemm_bf16_tn(tensors[0], b, out=out, config=cfg)
     else:
         host = [torch.from_numpy(x.view(np.int16)).view(torch.float16).pin_memory() for x in inputs]
         dev_in = [t.to(dev) for t in host]
@@ -300,17 +316,28 @@ def run_gpu(args):
         peak = peaks["bf16_tflops"]
         h2d = sum(t.numel() * t.element_size() for t in host)
         d2h = host_out.numel() * host_out.element_size()
+        if w.get("bound") == "hbm":
+            nbytes = 2.0 * (w["M"] * w["K"] + w["N"] * w["K"] + w["M"] * w["N"])
+            gbs = nbytes / (ms_per_step * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": gbs / peaks["hbm_gbs"], "peak_source": f"{peaks['source']} hbm_gbs (copy)",
+                        "frac_of_nominal_8000": gbs / 8000.0, "traffic": DRAM_TRAFFIC_BYTES.get(args.workload)}
+            l2_note = "B rotated over %d copies (%d MB) so no step finds it in L2" % (
+                w["rotate"], w["rotate"] * w["N"] * w["K"] * 2 // 2 ** 20)
+        else:
+            roofline = {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s",
+                        "frac": per_gpu_tflops / peak, "peak_source": f"{peaks['source']} bf16_tflops (burst)",
+                        "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
+                        "traffic": DRAM_TRAFFIC_BYTES.get(args.workload)}
+            l2_note = "inputs larger than L2, no flush between steps"
         line = {
             "metric": metric_name(w), "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16" if w["kind"] == "gemm" else "fp16", "data": "synthetic",
             "config": {"workload": w["desc"], "kernel_config": cfg_name,
                        "parallelism": "1 gpu" if world == 1 else f"{world} ranks, one problem slab per rank, no collective",
-                       "l2": "inputs larger than L2, no flush between steps"},
-            "roofline": {"bound": "tensor", "achieved": per_gpu_tflops, "peak": peak, "unit": "TFLOP/s",
-                         "frac": per_gpu_tflops / peak, "peak_source": f"{peaks['source']} bf16_tflops (burst)",
-                         "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
-                         "traffic": DRAM_TRAFFIC_BYTES.get(args.workload)},
+                       "l2": l2_note},
+            "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "gpu_launches": args.steps,

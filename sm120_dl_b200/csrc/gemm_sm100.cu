@@ -352,7 +352,7 @@ struct SplitKTraits {
     static constexpr int kBarrierBytes = (2 * STAGES + 1) * 8 + 16;
     static constexpr int kSmemBytes = kRingBytes + kBarrierBytes + 1024;
     static constexpr int kTmemCols = tmem_cols_for(BN);
-    static_assert(BN == 64 || BN == 128, "split-K tiles are 128 x 64 or 128 x 128");
+    static_assert(BN == 64 || BN == 128 || BN == 256, "split-K tiles are 128 x 64, 128 x 128 or 128 x 256");
     static_assert(kPartialBytes <= kRingBytes, "the partial tile must fit over the ring");
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB shared-memory limit of sm_100");
 };
@@ -650,20 +650,54 @@ int launch_gemm_splitk(const DeviceInfo* dev, const b200_gemm_config& cfg, int M
     return B200_OK;
 }
 
+// Clusters of `split` CTAs of this kernel the current device can hold at once (a cluster must
+// fit inside one GPC, so 8-CTA clusters leave SMs unused), or 0 when it cannot be asked.
+template <int BN, int STAGES>
+int splitk_active_clusters(int split) {
+    using T = SplitKTraits<BN, STAGES>;
+    static int cached[9] = {};
+    if (split < 1 || split > 8) return 0;
+    if (cached[split] != 0) return cached[split] > 0 ? cached[split] : 0;
+    auto kernel = gemm_splitk_kernel<BN, STAGES>;
+    int n = 0;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(static_cast<unsigned>(split * 148), 1, 1);
+    lc.blockDim = dim3(kThreads, 1, 1);
+    lc.dynamicSmemBytes = T::kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = static_cast<unsigned>(split);
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kernel, &lc) != cudaSuccess || n <= 0) {
+        (void)cudaGetLastError();  // no usable device: the caller falls back to an estimate
+        cached[split] = -1;
+        return 0;
+    }
+    cached[split] = n;
+    return n;
+}
+
+using ClustersFn = int (*)(int);
+
 struct Entry {
     b200_gemm_config cfg;
     LaunchFn launch;
+    ClustersFn active_clusters;   // split-K entries only
 };
 
 #define B200_GEMM_CONFIG(NAME, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)                                  \
     Entry{b200_gemm_config{NAME, kCtaM * CTA_GROUP, BN, kBK, STAGES, CTA_GROUP, ACC_BUFS, BS_W,        \
                            GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kSmemBytes,                    \
                            GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kTmemCols, 1},                 \
-          &launch_gemm<BN, STAGES, CTA_GROUP, ACC_BUFS>},
+          &launch_gemm<BN, STAGES, CTA_GROUP, ACC_BUFS>, nullptr},
 #define B200_GEMM_SPLITK_CONFIG(NAME, BN, STAGES, SPLIT_K)                                             \
     Entry{b200_gemm_config{NAME, kCtaM, BN, kBK, STAGES, 1, 1, 1, SplitKTraits<BN, STAGES>::kSmemBytes, \
                            SplitKTraits<BN, STAGES>::kTmemCols, SPLIT_K},                              \
-          &launch_gemm_splitk<BN, STAGES>},
+          &launch_gemm_splitk<BN, STAGES>, &splitk_active_clusters<BN, STAGES>},
 
 const Entry kEntries[] = {
 #include "generated/gemm_configs.inc"
@@ -748,11 +782,15 @@ int b200_gemm_find_config(const char* name) {
 }
 
 int b200_gemm_default_config(int M, int N, int K) {
-    // Cost model in units of "one k-block of a 128 x 256 CTA tile at full tensor rate":
-    //   waves of CTA groups over the 148 SMs  x  k-blocks per CTA  x  tile width / efficiency
-    // with the measured efficiency of each MMA width (a 128 x N x 16 MMA costs >= ~74 cycles
-    // whatever N is: 8192^3 runs at 1.55 / 1.11 / 0.67 PFLOP/s with N = 256 / 128 / 64), plus a per-tile epilogue and, for split-K, the cluster reduction.  Work on
-    // a ragged edge is paid like any other, so oversized tiles lose by themselves.
+    // Cost model in microseconds, fitted to measurements on a B200:
+    //   waves over the SMs  x  k-blocks per CTA  x  time of one k-block  +  fixed costs.
+    // One k-block of a 128 x BN CTA tile takes 0.22 / 0.29 / 0.36 / 0.43 us of tensor work for
+    // BN = 64 / 128 / 192 / 256 (a 128 x N x 16 MMA costs >= ~74 cycles whatever N is;
+    // 8192^3 runs at 0.67 / 1.11 / 1.55 PFLOP/s with BN = 64 / 128 / 256), a CTA pair
+    // saves ~6 % at BN = 256.  Where the tiles do not fill the GPU the loads bound it instead:
+    // ~95 GB/s per CTA, ~11.5 TB/s from L2 in total.  Split-K pays ~8 us for the cluster
+    // epilogue (12 us for 8-CTA clusters), and its waves are counted in clusters the device
+    // can hold at once.  Work on a ragged edge is paid like any other.
     if (M <= 0 || N <= 0 || K <= 0) return -1;
     int best = -1;
     double best_cost = 0.0;
@@ -761,17 +799,28 @@ int b200_gemm_default_config(int M, int N, int K) {
         const long tiles = static_cast<long>((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
         const long kb = (K + c.bk - 1) / c.bk;
         if (c.split_k > 1 && (tiles >= 148 || kb / c.split_k < 16)) continue;  // see b200dl.h
-        const long groups = tiles * c.split_k;                // CTA pairs, CTAs or split-K CTAs
-        const long slots = 148 / c.cta_group;
-        const long waves = (groups + slots - 1) / slots;
-        // the CTA pair halves each CTA's B traffic but pays a pair handshake per tile: worth it
-        // only on a full GPU
-        const double eff = (c.bn >= 256 ? 1.0 : c.bn >= 192 ? 0.90 : c.bn >= 128 ? 0.72 : 0.43) *
-                           (c.cta_group == 2 ? (tiles >= 74 ? 1.03 : 0.99) : 1.0);
+        long slots = 148 / c.cta_group;   // CTA pairs or CTAs resident at once
+        if (c.split_k > 1) {
+            const int held = b200::kEntries[i].active_clusters(c.split_k);
+            slots = held > 0 ? held : (c.split_k == 8 ? 14 : 144 / c.split_k);
+        }
+        const long waves = (tiles + slots - 1) / slots;
+        const long ctas = tiles * c.cta_group * c.split_k;
+        const long active = ctas < 148 ? ctas : 148;
+        double t_kb = c.bn >= 256 ? (c.cta_group == 2 ? 0.40 : 0.43) : c.bn >= 192 ? 0.36 : c.bn >= 128 ? 0.29 : 0.22;
+        if (ctas < 148 || c.split_k > 1) {
+            const double bytes = (128.0 + c.bn / c.cta_group) * 128.0;                 // A and B rows of one k-block
+            const double gbs = 95.0 < 11500.0 / active ? 95.0 : 11500.0 / active;       // per CTA
+            const double t_mem = bytes / (gbs * 1e3);
+            if (t_mem > t_kb) t_kb = t_mem;
+        }
         const double kb_per_cta = static_cast<double>((kb + c.split_k - 1) / c.split_k);
         // persistent kernels overlap all but the last epilogue with the next tile's mainloop
-        const double epilogue = c.split_k > 1 ? waves * (8.0 + 2.0 * c.split_k) : (c.acc_bufs > 1 ? 4.0 : 4.0 * waves);
-        double cost = waves * kb_per_cta * (c.bn / 256.0) / eff + epilogue;
+        const double fixed = c.split_k > 1 ? (c.split_k == 8 ? 12.0 : 8.0 + 0.25 * c.split_k)
+                                           : (c.acc_bufs > 1 ? 4.0 : 4.0 + 1.5 * (waves - 1)) +
+                                                 // the pair handshake per tile shows on latency-bound problems
+                                                 ((c.cta_group == 2 && tiles < 74) ? 1.0 : 0.0);
+        double cost = waves * kb_per_cta * t_kb + fixed;
         // ties: deeper ring, strip width 8 (fastest measured on 8192^3)
         cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == 8 ? 0.0002 : 0.0);
         if (best < 0 || cost < best_cost) {

@@ -115,7 +115,7 @@ def generate_configs(max_smem_kb, full=False):
     return configs
 
 
-SPLITK_BN_VALUES = (64, 128)
+SPLITK_BN_VALUES = (64, 128, 256)
 SPLITK_VALUES = (2, 4, 8)          # cluster sizes; 8 is the portable maximum
 
 

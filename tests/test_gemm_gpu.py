@@ -275,7 +275,7 @@ def test_split_k_skinny_shape_and_refusals(env):
             out = torch.empty((M, 64), dtype=torch.bfloat16, device=dev)
             rc = lib.b200_gemm_bf16_tn(i, M, 64, 192, a.data_ptr(), K, b.data_ptr(), K, out.data_ptr(), 64, None)
             assert rc == -2 and b"fewer 64-element blocks" in lib.b200_last_error()
-    assert ran == 6
+    assert ran == 9
 
 
 def test_split_k_ragged_shape_fp16_and_two_destinations(env):

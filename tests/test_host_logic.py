@@ -58,7 +58,7 @@ def test_gemm_generator_writes_reference_style_cmake(tmp_path):
     assert "set(GEMM_TN_DEFAULT_CONFIG" in text
     splitk = g.generate_splitk_configs(200)
     assert inc.read_text().count("B200_GEMM_CONFIG(\"") == len(cfgs)
-    assert inc.read_text().count("B200_GEMM_SPLITK_CONFIG(\"") == len(splitk) == 6
+    assert inc.read_text().count("B200_GEMM_SPLITK_CONFIG(\"") == len(splitk) == 9
     assert reg.read_text().count("B200_GEMM_ENTRY(") == len(cfgs) + len(splitk) + 1  # + the comment line
     for name, bn, stages, split_k in splitk:
         assert name == g.splitk_config_name(bn, stages, split_k) and split_k in (2, 4, 8)

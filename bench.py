@@ -60,7 +60,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised
 # under profiles/ (null until a capture of that kernel exists).  fa_d128: the capture is the
 # batch-1 slice of the workload (116.1 MB); traffic grows with the batch, so x4.
-DRAM_TRAFFIC_BYTES = {"gemm8192": 1.224e9, "fa_d128": 4 * 116.1e6, "fa_d64": None, "gemm_skinny": None}
+DRAM_TRAFFIC_BYTES = {"gemm8192": 1.224e9, "fa_d128": 4 * 116.1e6, "fa_d64": None, "gemm_skinny": 124.7e6}
 
 
 def flops_per_step(w):

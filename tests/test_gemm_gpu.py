@@ -298,3 +298,25 @@ def test_split_k_ragged_shape_fp16_and_two_destinations(env):
         torch.cuda.synchronize()
         want = (ah.double() @ bh.double().T)
         assert (ch.double() - want).abs().max().item() <= 2e-3 * max(1.0, want.abs().max().item())
+
+
+def test_split_k_leading_dimensions_several_row_tiles_ragged_k(env):
+    """Split-K with padded operands (lda, ldb > K), a column slab of a wider C (ldc > N),
+    several row tiles, an N no tile divides and a K that ends inside a k-block."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = 320, 200, 2048 + 24
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 23)
+    ref = oracle.gemm_f64(a_bits, b_bits)
+    a_pad = torch.full((M, K + 8), float("nan"), dtype=torch.bfloat16, device=dev)
+    b_pad = torch.full((N, K + 16), float("nan"), dtype=torch.bfloat16, device=dev)
+    a_pad[:, :K] = _to_dev(torch, a_bits, dev, torch.bfloat16)
+    b_pad[:, :K] = _to_dev(torch, b_bits, dev, torch.bfloat16)
+    for name in ("bf16_bm128_bn64_bk64_s8_cta1_splitk2", "bf16_bm128_bn128_bk64_s6_cta1_splitk4",
+                 "bf16_bm128_bn256_bk64_s4_cta1_splitk8"):
+        wide = torch.full((M, 512), -7.0, dtype=torch.bfloat16, device=dev)
+        idx = lib.b200_gemm_find_config(name.encode())
+        assert idx >= 0, name
+        _run(env, idx, a_pad, b_pad, M, N, K, c=wide[:, 104:104 + N], lda=K + 8, ldb=K + 16, ldc=512)
+        _check(oracle, wide[:, 104:104 + N].float().cpu().numpy(), ref)
+        # nothing outside the slab was touched
+        assert bool((wide[:, :104] == -7.0).all()) and bool((wide[:, 104 + N:] == -7.0).all()), name

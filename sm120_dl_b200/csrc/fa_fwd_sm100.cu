@@ -9,8 +9,8 @@
 //
 //   one CTA = two 128-row query tiles of one (batch, head); key/value blocks of 128 rows
 //   warp 0  (1 thread)  TMA: Q tiles once, then K_0, V_0, K_1, V_1, ... into a STAGES-deep ring
-//   warp 1  (1 thread)  tcgen05.mma: S_i = Q_i K_j^T (smem x smem -> tensor memory) and
-//                       O_i += P_i V_j (P read from tensor memory, V MN-major from smem),
+//   warp 1  (elected    tcgen05.mma: S_i = Q_i K_j^T (smem x smem -> tensor memory) and
+//            lane)      O_i += P_i V_j (P read from tensor memory, V MN-major from smem),
 //                       interleaved so tile 1's MMAs run while tile 0's softmax runs
 //   warps 4-7, 8-11     one softmax warpgroup per query tile, one thread per row: reads S_i
 //                       from tensor memory, running max / sum in registers, writes P_i

@@ -6,8 +6,8 @@
 // (utils/tools.h:30-40).  Everything below that contract is new:
 //
 //   warp 0  (1 thread)  TMA producer: A and B k-blocks -> STAGES-deep shared-memory ring
-//   warp 1  (1 thread)  issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32) from the
-//                       128B-swizzled ring into a tensor-memory accumulator; with
+//   warp 1  (elected    issues tcgen05.mma (kind::f16, bf16 x bf16 -> fp32) from the
+//            lane)      128B-swizzled ring into a tensor-memory accumulator; with
 //                       CTA_GROUP = 2 one instruction spans the CTA pair: 256 x BN x 16,
 //                       A rows and B rows split across the two CTAs' shared memory
 //   warps 2-5           epilogue: tcgen05.ld -> fp32->bf16 -> swizzled smem -> TMA store,
@@ -17,6 +17,9 @@
 // Shared-memory ring slots are released by tcgen05.commit onto the leader CTA's "empty"
 // barriers; the leader's producer relays each release to the peer CTA with a remote
 // mbarrier arrive, so no multicast form of any instruction is used.
+//
+// A second kernel, gemm_splitk_kernel, serves shapes with too few tiles to occupy the GPU: a
+// cluster of CTAs shares one tile along K and sums its partials through distributed shared memory.
 #include <cstdio>
 #include <cstring>
 #include <mutex>

@@ -38,10 +38,11 @@ constexpr int kBoxBytes = 128 * 128;      // one TMA box: 128 rows x 64 fp16 (12
 constexpr int kMaxDst = 8;                // copies of O one launch can write (one per GPU of a box)
 constexpr float kRescaleLog2 = 8.0f;      // rescale O only when the max grew by > 2^8
 // P V of a block is issued in two parts, 16-key MMA steps [0, kSplitP) and [kSplitP, 8): the
-// first starts while the softmax warps still work on the last keys, so only the short
-// second part and the next S stand between two softmax passes of a tile.
-constexpr int kSplitP = 6;
-static_assert(kSplitP == 2 || kSplitP == 4 || kSplitP == 6, "parts end on 32-key chunks");
+// first starts while the softmax warps still work on the remaining keys.  Measured on one
+// box, B4 H32 S4096 D128 / B16 H32 S2048 D64, TFLOP/s: first part of 32 keys 1210 / 667,
+// 64 keys 1194 / 665, 96 keys 1192 / 650, no split (kSplitP = 0) 1197 / 634.
+constexpr int kSplitP = 2;
+static_assert(kSplitP == 0 || kSplitP == 2 || kSplitP == 4 || kSplitP == 6, "parts end on 32-key chunks; 0 = one hand-off");
 // Register budget after the role split.  setmaxnreg.inc blocks until the CTA's own pool
 // (registers per thread at launch x threads) can supply the increase, so the two budgets
 // must fit in what the CTA was launched with or the kernel never gets past the split.
@@ -325,15 +326,17 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 bool have_k = false;
                 for (int i = 0; i < 2 && ok; ++i) {
                     if (j >= nblk[i]) continue;
-                    ok = wait(p_full + 16 * i, p_ph[i], 0x1230u + i);
-                    if (!ok) break;
-                    tc_fence_after();
-                    issue_pv_half(i, 0, v_addr, j > 0);
+                    if constexpr (kSplitP > 0) {
+                        ok = wait(p_full + 16 * i, p_ph[i], 0x1230u + i);
+                        if (!ok) break;
+                        tc_fence_after();
+                        issue_pv_half(i, 0, v_addr, j > 0);
+                    }
                     ok = wait(p_full + 16 * i + 8, p_ph[i], 0x1238u + i);
                     if (!ok) break;
                     p_ph[i] ^= 1u;
                     tc_fence_after();
-                    issue_pv_half(i, 1, v_addr, true);
+                    issue_pv_half(i, 1, v_addr, kSplitP > 0 || j > 0);
                     if (j + 1 < nblk[i]) {
                         if (!have_k) {
                             ok = wait(kv_full + 8 * s, ph, 0x1240u + s);
@@ -456,7 +459,7 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
                 }
                 // 32 keys = 16 packed columns; S is already in registers, so P may overwrite it.
                 tmem_st_32x32b_x16(t_s + c * 16, pr);
-                if (c == kSplitP / 2 - 1 || c == 3) {
+                if ((kSplitP > 0 && c == kSplitP / 2 - 1) || c == 3) {
                     // The first part (or all) of P is in tensor memory: let the MMA warp start on it.
                     tmem_wait_st();
                     tc_fence_before();

@@ -240,7 +240,7 @@ def run_gpu(args):
         host = [torch.from_numpy(x.view(np.int16)).view(torch.bfloat16).pin_memory() for x in inputs]
         dev_in = [t.to(dev) for t in host]
         out = torch.empty((w["M"], w["N"]), dtype=torch.bfloat16, device=dev)
-        cfg = ops.gemm_config_index(None, w["M"], w["N"], w["K"])
+        cfg = ops.gemm_config_index(args.kernel_config, w["M"], w["N"], w["K"])
         cfg_name = capi.gemm_configs()[cfg]["name"]
 
         # rotated copies of B for workloads smaller than L2 (kernel-only timing)
@@ -257,7 +257,7 @@ def run_gpu(args):
         host = [torch.from_numpy(x.view(np.int16)).view(torch.float16).pin_memory() for x in inputs]
         dev_in = [t.to(dev) for t in host]
         out = torch.empty((w["B"], w["S"], w["H"], w["D"]), dtype=torch.float16, device=dev)
-        cfg = ops.fa_config_index(None, w["D"])
+        cfg = ops.fa_config_index(args.kernel_config, w["D"])
         cfg_name = capi.fa_configs()[cfg]["name"]
 
         def step(tensors):
@@ -399,6 +399,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="gemm8192")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--kernel-config", default=None, help="config name instead of the library's default for the shape")
     ap.add_argument("--no-cpu-baseline", action="store_true", help="skip the CPU leg (N=1 only has it anyway)")
     args = ap.parse_args()
     if args.steps < 1:

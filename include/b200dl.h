@@ -115,7 +115,7 @@ int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, in
  * Replaces `kFlashFwdConfigs[] / kFlashFwdConfigCount / kFlashFwdDefaultConfigName`
  * (flashattention/v3_mMnNkN/pybind/flash_fwd_config_registry.hpp.in:7-30). */
 typedef struct b200_fa_config {
-    const char* name;   /* unique, e.g. "hd128_bm64_bn64_tq128x2_tk128_s3"                   */
+    const char* name;   /* unique, e.g. "hd128_bm64_bn64_tq128x2_tk128_s4_e0_r4"             */
     int head_dim;       /* 64 or 128                                                         */
     int block_m;        /* seq_len must be a multiple of this (query side)                   */
     int block_n;        /* seq_len must be a multiple of this (key side)                     */
@@ -125,6 +125,9 @@ typedef struct b200_fa_config {
     int stages;         /* depth of the K/V shared-memory ring                               */
     int nwarps;         /* warps per CTA                                                     */
     int smem_bytes;     /* dynamic shared memory per CTA                                     */
+    int softmax_layout; /* threads sharing one query row in the softmax: 4 = quad layout with
+                           a correction warpgroup and persistent CTAs, 1 = one thread per row
+                           that also rescales O, one CTA per 256 query rows                  */
 } b200_fa_config;
 
 int b200_fa_num_configs(void);

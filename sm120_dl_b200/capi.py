@@ -30,7 +30,7 @@ class FaConfig(ctypes.Structure):
     _fields_ = [("name", ctypes.c_char_p), ("head_dim", ctypes.c_int), ("block_m", ctypes.c_int),
                 ("block_n", ctypes.c_int), ("tile_q", ctypes.c_int), ("q_tiles", ctypes.c_int),
                 ("tile_kv", ctypes.c_int), ("stages", ctypes.c_int), ("nwarps", ctypes.c_int),
-                ("smem_bytes", ctypes.c_int)]
+                ("smem_bytes", ctypes.c_int), ("softmax_layout", ctypes.c_int)]
 
 
 EXPORTS = (

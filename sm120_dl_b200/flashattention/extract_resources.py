@@ -8,7 +8,8 @@ of libb200dl.so.  The log is what `python -m sm120_dl_b200.build lib --force --p
 prints (and stores as sm120_dl_b200/build/build.log).  Mangled kernel names are mapped back
 to config names:
 
-    fa_fwd_kernel<D, STAGES, EMU>                     -> hd{D}_..._s{STAGES}_e{EMU}
+    fa_fwd_ws_kernel<D, STAGES, EMU>                  -> hd{D}_..._s{STAGES}_e{EMU}_r4
+    fa_fwd_kernel<D, STAGES, EMU>                     -> hd{D}_..._s{STAGES}_e{EMU}_r1
     gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC>   -> bf16_bm{128*CTA_GROUP}_bn{BN}_bk64_s{STAGES}_cta{..}_acc{..}
                                                          (the raster width is a launch argument)
 
@@ -28,7 +29,7 @@ DEFAULT_OUTPUT = os.path.join(PACKAGE, "build", "resource.log")
 ENTRY = re.compile(r"Compiling entry function '([^']+)'")
 FRAME = re.compile(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads")
 USED = re.compile(r"Used (\d+) registers")
-FA_ARGS = re.compile(r"fa_fwd_kernelILi(\d+)ELi(\d+)ELi(\d+)EE")
+FA_ARGS = re.compile(r"fa_fwd(_ws)?_kernelILi(\d+)ELi(\d+)ELi(\d+)EE")
 GEMM_ARGS = re.compile(r"gemm_bf16_tn_kernelILi(\d+)ELi(\d+)ELi(\d+)ELi(\d+)EE")
 
 
@@ -40,8 +41,8 @@ def kernel_label(mangled):
             import flash_configs
         finally:
             sys.path.remove(HERE)
-        head_dim, stages, emu = (int(x) for x in m.groups())
-        return flash_configs.config_name(head_dim, stages, emu)
+        head_dim, stages, emu = (int(x) for x in m.groups()[1:])
+        return flash_configs.config_name(head_dim, stages, emu, 4 if m.group(1) else 1)
     m = GEMM_ARGS.search(mangled)
     if m:
         bn, stages, cta_group, acc = (int(x) for x in m.groups())

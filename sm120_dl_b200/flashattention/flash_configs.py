@@ -11,6 +11,14 @@ with Blackwell's vocabulary instead of mma.sync warp grids:
              tensor core works on one tile while the other tile's softmax runs
   tile_kv    128 key/value rows per ring slot
   stages     ring slots shared by K and V blocks (K_0, V_0, K_1, V_1, ...)
+  layout     how the softmax is laid over threads (the reference ships two warp layouts too,
+             v3_mMnNkN and v3_mMn1k1):
+               r4  four threads per query row (16 softmax warps), a correction warpgroup that
+                   rescales O and writes the output, persistent CTAs; one more shared-memory
+                   tile (output staging) and 24 warps
+               r1  one thread per query row (8 softmax warps) that also rescales O; one CTA
+                   per 256 query rows, 12 warps
+  emu        quarters of the exponentials evaluated by a polynomial on the FMA pipe
   block_m / block_n
              the sequence-length granularity the entry points accept (what the
              reference's harness checks with seq_len % block_m and % block_n); the kernel
@@ -28,12 +36,14 @@ TILE_Q = 128
 Q_TILES = 2
 TILE_KV = 128
 SEQ_GRANULARITY = 64
-STAGE_VALUES = {64: (8, 4), 128: (5, 3)}
+LAYOUTS = (1, 4)                                     # first = default
+STAGE_VALUES = {(64, 4): (8, 4), (128, 4): (4,), (64, 1): (8, 4), (128, 1): (5, 3)}
 # Quarters of the exponentials evaluated by a polynomial on the FMA pipe instead of the SFU
 # (the SFU's 16 ex2 per clock are the co-bottleneck at head_dim 128, the bottleneck at 64).
 EMU_VALUES = {64: (1, 0, 2), 128: (0, 1, 2)}   # first = default (fastest measured)
-NUM_WARPS = 12
+NUM_WARPS = {4: 24, 1: 12}
 DEFAULT_MAX_SMEM_KB = 227
+SMEM_LIMIT = DEFAULT_MAX_SMEM_KB * 1024
 TMEM_COLUMNS = 512
 
 
@@ -41,7 +51,13 @@ def tile_bytes(head_dim):
     return TILE_KV * head_dim * 2
 
 
-def smem_bytes(head_dim, stages):
+def smem_bytes(head_dim, stages, layout):
+    if layout == 4:
+        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], corr_full[2], o_ready[2],
+        # o_final[2], sum_full[2], sum_empty[2]; two [2][128] fp32 arrays; one staging tile
+        barriers = (2 + 2 * stages + 2 + 4 + 2 + 2 + 2 + 2 + 2) * 8 + 16
+        needed = (Q_TILES + stages + 1) * tile_bytes(head_dim) + 2 * 2 * TILE_Q * 4 + barriers
+        return min(needed + 1024, SMEM_LIMIT) if needed <= SMEM_LIMIT else needed
     barriers = (1 + 2 * stages + 2 + 4) * 8 + 16   # q_full, ring full/empty, s_full[2], p_full[2][2]
     return (Q_TILES + stages) * tile_bytes(head_dim) + barriers + 1024
 
@@ -50,33 +66,37 @@ def tmem_columns(head_dim):
     return Q_TILES * TILE_KV + Q_TILES * head_dim
 
 
-def config_name(head_dim, stages, emu):
+def config_name(head_dim, stages, emu, layout):
     return (f"hd{head_dim}_bm{SEQ_GRANULARITY}_bn{SEQ_GRANULARITY}_tq{TILE_Q}x{Q_TILES}_tk{TILE_KV}"
-            f"_s{stages}_e{emu}")
+            f"_s{stages}_e{emu}_r{layout}")
 
 
-def is_valid_config(head_dim, stages, max_smem):
+def is_valid_config(head_dim, stages, layout, max_smem):
     if head_dim not in HEAD_DIMS or stages < 3:   # V_j and K_{j+1} are live together, +1 to prefetch
+        return False
+    if layout not in LAYOUTS:
         return False
     if tmem_columns(head_dim) > TMEM_COLUMNS:
         return False
-    return smem_bytes(head_dim, stages) <= max_smem
+    return smem_bytes(head_dim, stages, layout) <= max_smem
 
 
 def generate_configs(max_smem_kb, only=None):
     max_smem = max_smem_kb * 1024
     configs = []
     for head_dim in HEAD_DIMS:
-        for stages in STAGE_VALUES[head_dim]:
-            if not is_valid_config(head_dim, stages, max_smem):
-                continue
-            # every polynomial share for the deepest ring, the first share only for the others
-            emus = EMU_VALUES[head_dim] if stages == STAGE_VALUES[head_dim][0] else EMU_VALUES[head_dim][:1]
-            for emu in emus:
-                name = config_name(head_dim, stages, emu)
-                if only and name not in only:
+        for layout in LAYOUTS:
+            stage_values = STAGE_VALUES[(head_dim, layout)]
+            for stages in stage_values:
+                if not is_valid_config(head_dim, stages, layout, max_smem):
                     continue
-                configs.append((name, head_dim, stages, emu, SEQ_GRANULARITY, SEQ_GRANULARITY))
+                # every polynomial share for the deepest ring, the first share only for the others
+                emus = EMU_VALUES[head_dim] if stages == stage_values[0] else EMU_VALUES[head_dim][:1]
+                for emu in emus:
+                    name = config_name(head_dim, stages, emu, layout)
+                    if only and name not in only:
+                        continue
+                    configs.append((name, head_dim, stages, emu, layout, SEQ_GRANULARITY, SEQ_GRANULARITY))
     return configs
 
 
@@ -112,9 +132,9 @@ def write_inc(path, configs, max_smem_kb):
     with _write_if_changed(path) as f:
         f.write("// Auto-generated by flash_configs.py - do not edit\n")
         f.write(f"// {len(configs)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
-        f.write("// B200_FA_CONFIG(name, HEAD_DIM, STAGES, EMU, BLOCK_M, BLOCK_N)\n")
-        for name, head_dim, stages, emu, bm, bn in configs:
-            f.write(f'B200_FA_CONFIG("{name}", {head_dim}, {stages}, {emu}, {bm}, {bn})\n')
+        f.write("// B200_FA_CONFIG(name, HEAD_DIM, STAGES, EMU, LAYOUT, BLOCK_M, BLOCK_N)\n")
+        for name, head_dim, stages, emu, layout, bm, bn in configs:
+            f.write(f'B200_FA_CONFIG("{name}", {head_dim}, {stages}, {emu}, {layout}, {bm}, {bn})\n')
 
 
 def write_registry(path, configs):
@@ -124,8 +144,8 @@ def write_registry(path, configs):
     with _write_if_changed(path) as f:
         f.write("// Auto-generated by flash_configs.py - do not edit\n")
         f.write("// B200_FA_ENTRY(index, name, HEAD_DIM, BLOCK_M, BLOCK_N, NWARPS, STAGES)\n")
-        for i, (name, head_dim, stages, emu, bm, bn) in enumerate(configs):
-            f.write(f'B200_FA_ENTRY({i}, "{name}", {head_dim}, {bm}, {bn}, {NUM_WARPS}, {stages})\n')
+        for i, (name, head_dim, stages, emu, layout, bm, bn) in enumerate(configs):
+            f.write(f'B200_FA_ENTRY({i}, "{name}", {head_dim}, {bm}, {bn}, {NUM_WARPS[layout]}, {stages})\n')
 
 
 def write_cmake(path, configs, max_smem_kb):
@@ -134,10 +154,10 @@ def write_cmake(path, configs, max_smem_kb):
         f.write("# Auto-generated by flash_configs.py - do not edit\n")
         f.write(f"set(FLASH_FWD_MAX_SMEM_BYTES {max_smem_kb * 1024})\n")
         f.write("set(FLASH_FWD_CONFIGS\n")
-        for name, head_dim, stages, emu, bm, bn in configs:
+        for name, head_dim, stages, emu, layout, bm, bn in configs:
             # head_dim|block_m|block_n|tile_q|q_tiles|tile_kv|nwarps|stage|smem_bytes|name
-            row = (head_dim, bm, bn, TILE_Q, Q_TILES, TILE_KV, NUM_WARPS, stages,
-                   smem_bytes(head_dim, stages), name)
+            row = (head_dim, bm, bn, TILE_Q, Q_TILES, TILE_KV, NUM_WARPS[layout], stages,
+                   smem_bytes(head_dim, stages, layout), name)
             f.write('    "' + "|".join(str(x) for x in row) + '"\n')
         f.write(")\n")
         f.write(f'set(FLASH_FWD_DEFAULT_CONFIG "{configs[0][0]}")\n')

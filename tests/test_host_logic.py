@@ -70,11 +70,15 @@ def test_flash_generator_rules(monkeypatch, tmp_path):
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     cfgs = f.generate_configs(227)
     assert {c[1] for c in cfgs} == {64, 128}
-    for name, hd, stages, emu, bm, bn in cfgs:
-        assert f.smem_bytes(hd, stages) <= 227 * 1024 and f.tmem_columns(hd) <= 512 and stages >= 3
-        assert 0 <= emu <= 3 and name == f.config_name(hd, stages, emu)
-    assert not f.is_valid_config(128, 6, 227 * 1024)   # 8 x 32 KiB tiles do not fit
-    assert not f.is_valid_config(256, 3, 227 * 1024)
+    assert {c[4] for c in cfgs} == {1, 4}              # both softmax layouts for every head_dim
+    assert {(c[1], c[4]) for c in cfgs} == {(64, 1), (64, 4), (128, 1), (128, 4)}
+    for name, hd, stages, emu, layout, bm, bn in cfgs:
+        assert f.smem_bytes(hd, stages, layout) <= 227 * 1024 and f.tmem_columns(hd) <= 512 and stages >= 3
+        assert 0 <= emu <= 3 and name == f.config_name(hd, stages, emu, layout)
+    assert not f.is_valid_config(128, 6, 1, 227 * 1024)   # 8 x 32 KiB tiles do not fit
+    assert not f.is_valid_config(128, 5, 4, 227 * 1024)   # nor do 2 + 5 + 1 (staging) of them
+    assert f.is_valid_config(128, 4, 4, 227 * 1024)
+    assert not f.is_valid_config(256, 3, 1, 227 * 1024)
     # the environment inputs of the reference generator still work
     monkeypatch.setenv("FLASH_FWD_ONLY_CONFIGS", cfgs[0][0])
     monkeypatch.setenv("FLASH_FWD_MAX_SMEM_KB", "227")
@@ -115,7 +119,8 @@ def test_config_tables_match_generators(lib):
     fc = capi.fa_configs()
     assert [c["name"] for c in fc] == [c[0] for c in f.generate_configs(227)]
     for c in fc:
-        assert c["smem_bytes"] == f.smem_bytes(c["head_dim"], c["stages"])
+        assert c["smem_bytes"] == f.smem_bytes(c["head_dim"], c["stages"], c["softmax_layout"])
+        assert c["nwarps"] == f.NUM_WARPS[c["softmax_layout"]]
 
 
 def test_config_lookup(lib):
@@ -256,5 +261,5 @@ def test_extract_resources_maps_kernels_to_config_names(tmp_path):
     assert mod.main([str(log), str(out)]) == 0
     lines = out.read_text().splitlines()
     assert lines[0] == "func_name spill stack registers"
-    assert lines[1] == "hd128_bm64_bn64_tq128x2_tk128_s5_e0 16 8 168"
+    assert lines[1] == "hd128_bm64_bn64_tq128x2_tk128_s5_e0_r1 16 8 168"
     assert lines[2] == "bf16_bm256_bn256_bk64_s6_cta2_acc2 0 0 96"

@@ -107,15 +107,24 @@ int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, in
  *   - All calls share the one array.  Each call clears it on `stream` before its kernel
  *     runs, so calls that overlap on the GPU (different streams) race on it: their results
  *     in C are still correct, but the recorded status is unreliable.  The block written by
- *     this variant is not reported by b200_device_status. */
+ *     this variant is not reported by b200_device_status; read it with
+ *     b200_gemm_noalloc_status. */
 int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda,
                               const void* B, int64_t ldb, void* C, int64_t ldc, void* stream);
+
+/* Synchronises the current device and copies out the status word the allocation-free GEMM
+ * keeps in its built-in array: 0 when the last b200_gemm_bf16_tn_noalloc launch on this device
+ * ran to completion, otherwise the code of the first bounded wait that gave up.  Like that
+ * entry point it allocates nothing (one 4-byte copy from the array's address) and has no
+ * counterpart in the reference.  The word is cleared by the next noalloc launch, not by
+ * this call. */
+int b200_gemm_noalloc_status(uint32_t* code);
 
 /* ------------------------------------------------------------- attention config registry
  * Replaces `kFlashFwdConfigs[] / kFlashFwdConfigCount / kFlashFwdDefaultConfigName`
  * (flashattention/v3_mMnNkN/pybind/flash_fwd_config_registry.hpp.in:7-30). */
 typedef struct b200_fa_config {
-    const char* name;   /* unique, e.g. "hd128_bm64_bn64_tq128x2_tk128_s4_e0_r4"             */
+    const char* name;   /* unique, e.g. "hd128_bm64_bn64_tq128x2_tk128_s4_e0_r2"             */
     int head_dim;       /* 64 or 128                                                         */
     int block_m;        /* seq_len must be a multiple of this (query side)                   */
     int block_n;        /* seq_len must be a multiple of this (key side)                     */
@@ -125,9 +134,9 @@ typedef struct b200_fa_config {
     int stages;         /* depth of the K/V shared-memory ring                               */
     int nwarps;         /* warps per CTA                                                     */
     int smem_bytes;     /* dynamic shared memory per CTA                                     */
-    int softmax_layout; /* threads sharing one query row in the softmax: 4 = quad layout with
-                           a correction warpgroup and persistent CTAs, 1 = one thread per row
-                           that also rescales O, one CTA per 256 query rows                  */
+    int softmax_layout; /* threads sharing one query row in the softmax: 2 = with a correction
+                           warpgroup and persistent CTAs, 1 = one thread per row that also
+                           rescales O, one CTA per 256 query rows                            */
 } b200_fa_config;
 
 int b200_fa_num_configs(void);

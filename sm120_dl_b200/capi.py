@@ -35,7 +35,8 @@ class FaConfig(ctypes.Structure):
 
 EXPORTS = (
     "b200_gemm_num_configs", "b200_gemm_get_config", "b200_gemm_find_config",
-    "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_f16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_bf16_tn_scatter",
+    "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_f16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_noalloc_status",
+    "b200_gemm_bf16_tn_scatter",
     "b200_fa_num_configs", "b200_fa_get_config", "b200_fa_find_config",
     "b200_fa_default_config", "b200_fa_fwd_fp16", "b200_fa_fwd_fp16_scatter",
     "b200_last_error", "b200_device_status", "b200_version",
@@ -73,6 +74,8 @@ def lib():
                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, i64, vp]
     L.b200_gemm_bf16_tn_noalloc.restype = ctypes.c_int
     L.b200_gemm_bf16_tn_noalloc.argtypes = L.b200_gemm_bf16_tn.argtypes
+    L.b200_gemm_noalloc_status.restype = ctypes.c_int
+    L.b200_gemm_noalloc_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
     if not hasattr(L, "b200_fa_fwd_fp16"):
         raise ImportError(f"{LIB_PATH} does not export the attention entry points; rebuild it")
     L.b200_fa_num_configs.restype = ctypes.c_int
@@ -119,6 +122,14 @@ def gemm_configs():
 def fa_configs():
     L = lib()
     return [_cfg_dict(L.b200_fa_get_config(i).contents) for i in range(L.b200_fa_num_configs())]
+
+
+def noalloc_status():
+    """Synchronise the current device; return the status word of the allocation-free GEMM's
+    built-in scratch array (0 = its last launch ran to completion)."""
+    code = ctypes.c_uint32(0)
+    check(lib().b200_gemm_noalloc_status(ctypes.byref(code)))
+    return code.value
 
 
 def device_status():

@@ -5,8 +5,8 @@
 // (batch, head) on [B,S,H,D] fp16 tensors.  Two kernel layouts implement it (the reference
 // ships two warp layouts as well, v3_mMnNkN and v3_mMn1k1):
 //
-//   r4  fa_fwd_ws.cuh         persistent CTAs; load, MMA, softmax and correction warpgroups;
-//                             four softmax threads per query row
+//   r2  fa_fwd_ws.cuh         persistent CTAs; load, MMA, softmax and correction warpgroups;
+//                             two softmax threads per query row
 //   r1  fa_fwd_rowthread.cuh  one CTA per 256 query rows; one softmax thread per row, which
 //                             also rescales O
 //
@@ -14,7 +14,6 @@
 // the last key block is masked, and stores are clipped by the tensor map.
 #include <cmath>
 #include <cstring>
-#include <mutex>
 
 #include "fa_fwd_rowthread.cuh"
 #include "fa_fwd_ws.cuh"
@@ -38,19 +37,6 @@ int make_tmap(CUtensorMap* out, const void* base, int batch, int seq, int heads,
                             static_cast<uint64_t>(strides[0]) * 2};
     const uint32_t box[4] = {64, static_cast<uint32_t>(box_rows), 1, 1};
     return encode_tmap_2byte(out, base, 4, dims, sb, box, true);
-}
-
-// cudaFuncAttributeMaxDynamicSharedMemorySize is set once per (kernel, device).
-template <typename Kernel>
-int set_smem_once(Kernel kernel, int smem_bytes, int device, bool (&done)[64], const char* name) {
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    if (done[device]) return B200_OK;
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess)
-        return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", name, smem_bytes, cudaGetErrorString(e));
-    done[device] = true;
-    return B200_OK;
 }
 
 int gcd_int(int a, int b) {
@@ -78,7 +64,7 @@ int launch_fa_r1(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
     for (int d = 0; d < n_dst; ++d) {
         if (int rc = make_tmap(&to.m[d], o_list[d], batch, seq_q, heads, D, os, 128)) return rc;
     }
-    static bool attr_done[64] = {};
+    static bool attr_done[kMaxDevices] = {};
     if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
     const int q_pairs = (seq_q + kQTiles * kTileQ - 1) / (kQTiles * kTileQ);
     if (heads > 65535 || batch > 65535) return fail(B200_ESHAPE, "heads and batch must be <= 65535");
@@ -92,7 +78,7 @@ int launch_fa_r1(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
 }
 
 template <int D, int STAGES, int EMU>
-int launch_fa_r4(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
+int launch_fa_r2(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
                  void* const* o_list, int n_dst, int batch, int seq_q, int seq_k, int heads, const int64_t* qs,
                  const int64_t* ks, const int64_t* vs, const int64_t* os, float softmax_scale, int causal,
                  cudaStream_t stream) {
@@ -108,7 +94,7 @@ int launch_fa_r4(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
         // each correction warp stores its own 32 rows of a finished tile
         if (int rc = make_tmap(&to.m[d], o_list[d], batch, seq_q, heads, D, os, 32)) return rc;
     }
-    static bool attr_done[64] = {};
+    static bool attr_done[kMaxDevices] = {};
     if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
     const int q_pairs = (seq_q + kQTiles * kTileQ - 1) / (kQTiles * kTileQ);
     const long units = static_cast<long>(q_pairs) * heads * batch;
@@ -130,13 +116,13 @@ int launch_fa_r4(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
 
 template <int D, int STAGES, int EMU, int LAYOUT>
 constexpr FaLaunchFn fa_launcher() {
-    static_assert(LAYOUT == 1 || LAYOUT == 4, "softmax layout is 1 (thread per row) or 4 (quad per row)");
-    if constexpr (LAYOUT == 4) return &launch_fa_r4<D, STAGES, EMU>;
+    static_assert(LAYOUT == 1 || LAYOUT == 2, "softmax layout is 1 or 2 threads per query row");
+    if constexpr (LAYOUT == 2) return &launch_fa_r2<D, STAGES, EMU>;
     else return &launch_fa_r1<D, STAGES, EMU>;
 }
 template <int D, int STAGES, int LAYOUT>
 constexpr int fa_smem_bytes() {
-    if constexpr (LAYOUT == 4) return FaWsTraits<D, STAGES>::kSmemBytes;
+    if constexpr (LAYOUT == 2) return FaWsTraits<D, STAGES>::kSmemBytes;
     else return FaTraits<D, STAGES>::kSmemBytes;
 }
 
@@ -147,7 +133,7 @@ struct FaEntry {
 
 #define B200_FA_CONFIG(NAME, D, STAGES, EMU, LAYOUT, BLOCK_M, BLOCK_N)                                        \
     FaEntry{b200_fa_config{NAME, D, BLOCK_M, BLOCK_N, kTileQ, kQTiles, kTileKV, STAGES,                        \
-                           (LAYOUT == 4 ? kWsThreads : kFaThreads) / 32, fa_smem_bytes<D, STAGES, LAYOUT>(),   \
+                           (LAYOUT == 2 ? kWsThreads : kFaThreads) / 32, fa_smem_bytes<D, STAGES, LAYOUT>(),   \
                            LAYOUT},                                                                            \
             fa_launcher<D, STAGES, EMU, LAYOUT>()},
 
@@ -222,5 +208,14 @@ int b200_fa_fwd_fp16(int config, const void* q, const void* k, const void* v, vo
     return b200_fa_fwd_fp16_scatter(config, q, k, v, &o, 1, batch, seq_q, seq_k, heads, head_dim, q_strides, k_strides,
                                     v_strides, o_strides, softmax_scale, causal, stream);
 }
+
+#ifdef B200_FA_PROFILE
+// Profiling builds only: the cycle counters CTA 0 of the last r2 launch recorded.
+int b200_fa_profile_read(unsigned long long* out32) {
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out32, b200::g_fa_profile, 32 * sizeof(unsigned long long));
+    return e == cudaSuccess ? B200_OK : b200::fail(B200_ECUDA, "reading the profile counters: %s", cudaGetErrorString(e));
+}
+#endif
 
 }  // extern "C"

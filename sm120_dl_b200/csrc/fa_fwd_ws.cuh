@@ -1,4 +1,4 @@
-// Attention forward, layout "r4": warp-specialised load, MMA, softmax and correction
+// Attention forward, layout "r2": warp-specialised load, MMA, softmax and correction
 // warpgroups in a persistent CTA.
 //
 // Same arithmetic as the reference kernel flash_atten_v3_fwd
@@ -10,17 +10,18 @@
 //   warp 0  (1 thread)   TMA: per unit the two Q tiles, then K_0, V_0, K_1, V_1, ... into a ring
 //   warp 1  (elected     tcgen05.mma: S_i = Q_i K_j^T and O_i += P_i V_j for both query tiles
 //            lane)       of the unit, tile 1's MMAs running while tile 0's softmax runs
-//   warps 4-7            correction warpgroup, one thread per query row: multiplies O_i in
-//                        tensor memory by the factor the softmax warps publish when a row max
-//                        grew by more than 2^kRescaleLog2, and at the end of a unit turns
-//                        O_i / sum into fp16, stages it in shared memory and stores it with
-//                        TMA while the softmax warps already work on the next unit
-//   warps 8-15, 16-23    softmax of query tile 0 and 1, eight warps per tile.  A warp owns 16
-//                        rows; a row's 128 scores are spread over the four threads of a quad
-//                        (the m16n8 fragment layout of tcgen05.ld.16x256b), so a row max costs
-//                        two shuffles and a thread never holds more than 32 scores: first pass
-//                        row max, second pass exp2 / row sum / fp16 P written back over S in
-//                        tensor memory, handed to the MMA warp in two halves of 64 keys.
+//   warps 4-7            correction warpgroup, one thread per query row: follows the row maxima
+//                        the softmax warps publish, multiplies O_i in tensor memory by
+//                        2^(old max - new max) when a max grew by more than 2^kRescaleLog2, and
+//                        at the end of a unit turns O_i / sum into fp16, stages it in shared
+//                        memory and stores it with TMA while the softmax warps already work on
+//                        the next unit
+//   warps 8-15, 16-23    softmax of query tile 0 and 1, eight warps per tile, two threads per
+//                        row: a thread reads one half (64 keys) of its row of S from tensor
+//                        memory exactly once (tensor-memory reads are the scarce resource: a
+//                        warp gets ~48 bytes per clock), the two halves exchange their maxima
+//                        through shared memory, then exp2 / row sum / fp16 P written back
+//                        over S, handed to the MMA warp in two parts
 //
 // One unit = 256 query rows of one (batch, head).  CTAs walk the unit list with a static
 // stride; for causal problems the grid size is chosen coprime to the number of units per head
@@ -40,8 +41,8 @@ constexpr int kWsThreads = 768;           // 24 warps: 2 + 2 idle, 4 correction,
 // largest multiple of 8 that fits 64 K registers); the three budgets re-divide exactly that pool.
 constexpr int kWsRegsAtLaunch = 80;
 constexpr int kWsRegsLoadMma = 56;        // warps 0-3
-constexpr int kWsRegsCorrection = 72;     // warps 4-7
-constexpr int kWsRegsSoftmax = 88;        // warps 8-23
+constexpr int kWsRegsCorrection = 40;     // warps 4-7
+constexpr int kWsRegsSoftmax = 96;        // warps 8-23: 64 scores of a row live at once
 static_assert(kWsRegsLoadMma * 128 + kWsRegsCorrection * 128 + kWsRegsSoftmax * 512 <= kWsRegsAtLaunch * kWsThreads,
               "setmaxnreg budgets exceed the registers the CTA is launched with");
 constexpr int kSmemLimit = 232448;        // 227 KiB
@@ -50,16 +51,16 @@ template <int D, int STAGES>
 struct FaWsTraits {
     static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
     static constexpr int kBoxes = D / 64;
-    static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a Q tile, a K block, a V block or an O tile
+    static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a Q tile, a K block or a V block
     static constexpr int kNumBarriers = 2 + 2 * STAGES + 2 + 4 + 2 + 2 + 2 + 2 + 2;
-    static constexpr int kSmallBytes = 2 * kTileQ * 4 /* alpha */ + 2 * kTileQ * 4 /* totals */ + kNumBarriers * 8 + 16;
-    // data that must start on a 1024-byte boundary (128-byte swizzle), then the small arrays
-    static constexpr int kNeeded = (kQTiles + STAGES + 1) * kTileBytes + kSmallBytes;
-    static constexpr int kSmemBytes = (kNeeded + 1024 <= kSmemLimit) ? kNeeded + 1024 : kSmemLimit;
+    // row maxima [2 block parities][2 tiles][2 halves][128] and row sums [2 tiles][2 halves][128], fp32
+    static constexpr int kSmallBytes = 2 * 2 * 2 * kTileQ * 4 + 2 * 2 * kTileQ * 4 + kNumBarriers * 8 + 16;
+    // tiles first (they need 1024-byte alignment for the 128-byte swizzle): Q, ring, one staging box
+    static constexpr int kSmemBytes = (kQTiles + STAGES) * kTileBytes + kBoxBytes + kSmallBytes + 1024;
     static constexpr int kTmemCols = 512;
     static constexpr int kColS = 0;
     static constexpr int kColO = 256;
-    static_assert(kNeeded <= kSmemLimit, "exceeds the 227 KiB shared-memory limit of sm_100");
+    static_assert(kSmemBytes <= kSmemLimit, "exceeds the 227 KiB shared-memory limit of sm_100");
 };
 
 __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
@@ -97,6 +98,56 @@ __device__ __forceinline__ UnitCoord unit_coord(int id, int q_pairs, int heads, 
     return u;
 }
 
+// The running max a row's accumulators are scaled to moves only when the new maximum exceeds it
+// by more than 2^kRescaleLog2 (always on the first block).  Softmax and correction threads run
+// this same function on the same inputs, so they agree bit for bit.  Returns the factor
+// 2^((old - new) * scale) for what was accumulated so far (1 when the reference stays).
+__device__ __forceinline__ float advance_row_max(float& m, float block_max, float scale_log2) {
+    const float mn = fmaxf(m, block_max);
+    const bool need = (mn - m) * scale_log2 > kRescaleLog2 || m == -INFINITY;
+    if (!need) return 1.f;
+    const float alpha = (m == -INFINITY) ? 0.f : fast_exp2((m - mn) * scale_log2);
+    m = mn;
+    return alpha;
+}
+
+// P = exp2(s * scale - m * scale) for 16 scores of one row: adds the un-rounded values to the
+// row sum and packs fp16 pairs (packed column x holds keys 2x, 2x+1).  EMU of every 4 pairs
+// use the polynomial, the rest the SFU.
+template <int EMU>
+__device__ __forceinline__ void exp_16(const uint32_t* s, uint32_t (&pr)[8], f32x2 scale2, f32x2 nm2, f32x2& l,
+                                       const Exp2PolyConsts& poly) {
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        const f32x2 xs = fma2(pack2(__uint_as_float(s[2 * x]), __uint_as_float(s[2 * x + 1])), scale2, nm2);
+        f32x2 pp;
+        if ((x & 3) < EMU) {
+            pp = exp2_poly2(xs, poly);
+        } else {
+            float x0, x1;
+            unpack2(xs, x0, x1);
+            pp = pack2(fast_exp2(x0), fast_exp2(x1));
+        }
+        l = add2(l, pp);
+        float p0, p1;
+        unpack2(pp, p0, p1);
+        pr[x] = pack_f16x2(p0, p1);
+    }
+}
+
+#ifdef B200_FA_PROFILE
+// Cycle counters of CTA 0 (profiling builds only): [0..7] MMA warp, [8..15] softmax warp 8,
+// [16..23] softmax warp 16, [24..31] correction warp 4.
+__device__ unsigned long long g_fa_profile[32];
+#define FA_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned long long prof_t = clock64();
+#define FA_PROF(n) { const unsigned long long prof_now = clock64(); prof_acc[n] += prof_now - prof_t; prof_t = prof_now; }
+#define FA_PROF_DUMP(base) if (blockIdx.x == 0 && lane == 0) { for (int x = 0; x < 8; ++x) g_fa_profile[(base) + x] = prof_acc[x]; }
+#else
+#define FA_PROF_DECL
+#define FA_PROF(n) {}
+#define FA_PROF_DUMP(base) {}
+#endif
+
 template <int D, int STAGES, int EMU>
 __global__ void __launch_bounds__(kWsThreads, 1)
 fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
@@ -108,43 +159,27 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t q_smem = smem_base;                                  // [2] query tiles
     const uint32_t ring_smem = q_smem + kQTiles * T::kTileBytes;        // [STAGES] K / V blocks
-    const uint32_t o_smem = ring_smem + STAGES * T::kTileBytes;         // one O tile (staging for the TMA store)
-    const uint32_t alpha_smem = o_smem + T::kTileBytes;                 // [2][128] fp32: factor for O_i, per row
-    const uint32_t total_smem = alpha_smem + 2 * kTileQ * 4;            // [2][128] fp32: row sums of a finished unit
-    const uint32_t bar_base = total_smem + 2 * kTileQ * 4;
+    const uint32_t o_smem = ring_smem + STAGES * T::kTileBytes;         // one 128 x 64 box: staging for the O stores
+    const uint32_t max_smem = o_smem + kBoxBytes;                       // [2][2][2][128] fp32 row maxima of a block
+    const uint32_t sum_smem = max_smem + 2 * 2 * 2 * kTileQ * 4;        // [2][2][128] fp32 row sums of a finished unit
+    const uint32_t bar_base = sum_smem + 2 * 2 * kTileQ * 4;
     const uint32_t q_full = bar_base;                     // TMA -> MMA: the unit's Q tiles landed
     const uint32_t q_empty = q_full + 8;                  // MMA -> TMA: last S of the unit issued and complete
     const uint32_t kv_full = q_empty + 8;                 // [STAGES] TMA -> MMA
     const uint32_t kv_empty = kv_full + 8 * STAGES;       // [STAGES] MMA -> TMA
     const uint32_t s_full = kv_empty + 8 * STAGES;        // [2] MMA -> softmax: S_i ready
-    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: half h of P_i written
-    const uint32_t corr_full = p_full + 32;               // [2] softmax -> correction: factors of this block published
-    const uint32_t o_ready = corr_full + 16;              // [2] correction -> MMA: O_i may be accumulated into
+    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: part h of P_i written
+    const uint32_t max_full = p_full + 32;                // [2] softmax -> softmax, correction: the block's row maxima published
+    const uint32_t o_ready = max_full + 16;               // [2] correction -> MMA: O_i may be accumulated into
     const uint32_t o_final = o_ready + 16;                // [2] MMA -> correction: O_i of the unit complete
     const uint32_t sum_full = o_final + 16;               // [2] softmax -> correction: row sums published
     const uint32_t sum_empty = sum_full + 16;             // [2] correction -> softmax: row sums taken
     const uint32_t tmem_slot = sum_empty + 16;
     const uint32_t abort_slot = tmem_slot + 4;
-    uint8_t* smem_aligned = smem_raw + (smem_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_aligned + (tmem_slot - smem_base));
-    volatile uint32_t* abort_ptr = reinterpret_cast<volatile uint32_t*>(smem_aligned + (abort_slot - smem_base));
-    float* alpha_ptr = reinterpret_cast<float*>(smem_aligned + (alpha_smem - smem_base));
-    float* total_ptr = reinterpret_cast<float*>(smem_aligned + (total_smem - smem_base));
-    const WaitGuard guard{abort_ptr, status};
+    const WaitGuardS guard{abort_slot, status};
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-
-    {
-        // The layout above must fit behind the aligned base; it always does when the dynamic
-        // segment starts on a 1024-byte boundary.  Otherwise report and leave (uniformly).
-        uint32_t dyn_size;
-        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
-        if ((smem_base - smem_u32(smem_raw)) + static_cast<uint32_t>(T::kNeeded) > dyn_size) {
-            if (threadIdx.x == 0) atomicCAS(status, 0u, 0x80000000u | 0x1fffu);
-            return;
-        }
-    }
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -157,13 +192,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(s_full + 8 * i, 1);
             mbar_init(p_full + 16 * i, 8);       // one arrival per softmax warp of the tile
             mbar_init(p_full + 16 * i + 8, 8);
-            mbar_init(corr_full + 8 * i, 8);
+            mbar_init(max_full + 8 * i, 8);
             mbar_init(o_ready + 8 * i, 4);       // one arrival per correction warp
             mbar_init(o_final + 8 * i, 1);
             mbar_init(sum_full + 8 * i, 8);
             mbar_init(sum_empty + 8 * i, 4);
         }
-        *abort_ptr = 0;
+        st_shared_u32(abort_slot, 0);
         fence_mbar_init();
         prefetch_tensormap(&tmap_q);
         prefetch_tensormap(&tmap_k);
@@ -177,7 +212,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot_ptr;
+    const uint32_t tmem_base = ld_shared_u32(tmem_slot);
     const int first_unit = static_cast<int>(blockIdx.x);
     const int unit_stride = static_cast<int>(gridDim.x);
 
@@ -230,26 +265,37 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             uint32_t o_ph[2] = {0, 0};
             bool ok = true;
 
+            // Descriptors are built once per operand tile; a 16-element step along the head
+            // dimension (S) or 16 key rows (P V) is a constant added to the address field, so one
+            // MMA costs two 64-bit adds beside the instruction itself (the issuing warp shares
+            // its scheduler with four softmax warps).
+            const uint64_t q_desc0 = smem_desc_kmajor_sw128(q_smem);
+            const uint64_t q_desc1 = smem_desc_kmajor_sw128(q_smem + T::kTileBytes);
             auto issue_s = [&](int i, uint32_t k_addr) {
-                const uint32_t q_addr = q_smem + i * T::kTileBytes;
+                const uint64_t q_desc = i ? q_desc1 : q_desc0;
+                const uint64_t k_desc = smem_desc_kmajor_sw128(k_addr);
                 if (!elect_one()) return;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-                    mma_ss<1>(tmem_base + T::kColS + i * kTileKV, smem_desc_kmajor_sw128(q_addr + off),
-                              smem_desc_kmajor_sw128(k_addr + off), idesc_qk, kk > 0 ? 1u : 0u);
+                    constexpr int kBoxUnits = kBoxBytes >> 4;
+                    const uint64_t off = static_cast<uint64_t>((kk >> 2) * kBoxUnits + (kk & 3) * 2);
+                    mma_ss<1>(tmem_base + T::kColS + i * kTileKV, q_desc + off, k_desc + off, idesc_qk,
+                              kk > 0 ? 1u : 0u);
                 }
             };
-            // Half h of P V: 16-key steps [4h, 4h+4) of the block.  P: 16 keys = 8 packed columns.
-            // V: 16 key rows = 2048 bytes; the second 64-wide span of the head dimension lives
-            // one box (16 KiB) further.
-            auto issue_pv_half = [&](int i, int h, uint32_t v_addr, bool accumulate) {
+            // Part h of P V.  The two threads of a row work on keys [0,64) and [64,128) at the
+            // same time, so the first part is the first 32 keys of either half: 16-key steps
+            // {0,1,4,5}, the second part steps {2,3,6,7}.  P: 16 keys = 8 packed columns.  V: 16
+            // key rows = 2048 bytes; the second 64-wide span of the head dimension lives one box
+            // (16 KiB) further.
+            auto issue_pv_part = [&](int i, int h, uint64_t v_desc, bool accumulate) {
                 if (!elect_one()) return;
 #pragma unroll
-                for (int kk = 4 * h; kk < 4 * h + 4; ++kk) {
+                for (int x = 0; x < 4; ++x) {
+                    const int kk = (x >> 1) * 4 + 2 * h + (x & 1);
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
-                           smem_desc_mnmajor_sw128(v_addr + kk * 2048, kBoxBytes), idesc_pv,
-                           (accumulate || kk > 0) ? 1u : 0u);
+                           v_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
+                           (accumulate || x > 0) ? 1u : 0u);
                 }
             };
             auto commit = [&](uint32_t bar) {
@@ -260,20 +306,26 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 return __all_sync(0xffffffffu, mbar_wait(guard, bar, parity, site));
             };
 
+            FA_PROF_DECL
             for (int id = first_unit; id < num_units && ok; id += unit_stride) {
                 const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
+                FA_PROF(5)
                 ok = wait(q_full, q_ph, 0x1200u);
                 if (!ok) break;
+                FA_PROF(0)
                 q_ph ^= 1u;
                 // K_0
-                uint32_t k_addr = 0, v_addr = 0;
+                uint32_t k_addr = 0;
+                uint64_t v_desc = 0;
                 int k_slot = 0, v_slot = 0;
                 ok = wait(kv_full + 8 * s, ph, 0x1210u + s);
                 if (!ok) break;
+                FA_PROF(1)
                 k_addr = ring_smem + s * T::kTileBytes;
                 k_slot = s;
                 if (++s == STAGES) { s = 0; ph ^= 1u; }
                 tc_fence_after();
+#pragma unroll
                 for (int i = 0; i < 2; ++i) {
                     if (u.nblk[i] > 0) {
                         issue_s(i, k_addr);
@@ -284,30 +336,40 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (u.nmax == 1) commit(q_empty);
                 for (int j = 0; j < u.nmax && ok; ++j) {
                     // V_j
+                    FA_PROF(5)
                     ok = wait(kv_full + 8 * s, ph, 0x1220u + s);
                     if (!ok) break;
-                    v_addr = ring_smem + s * T::kTileBytes;
+                    FA_PROF(1)
+                    v_desc = smem_desc_mnmajor_sw128(ring_smem + s * T::kTileBytes, kBoxBytes);
                     v_slot = s;
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
                     bool have_k = false;
-                    for (int i = 0; i < 2 && ok; ++i) {
-                        if (j >= u.nblk[i]) continue;
+#pragma unroll
+                    for (int i = 0; i < 2; ++i) {
+                        if (!ok || j >= u.nblk[i]) continue;
+                        FA_PROF(5)
                         ok = wait(o_ready + 8 * i, o_ph[i], 0x1228u + i);
-                        if (!ok) break;
+                        if (!ok) continue;
+                        FA_PROF(2)
                         o_ph[i] ^= 1u;
                         ok = wait(p_full + 16 * i, p_ph[i], 0x1230u + i);
-                        if (!ok) break;
+                        if (!ok) continue;
+                        FA_PROF(3 + i)
                         tc_fence_after();
-                        issue_pv_half(i, 0, v_addr, j > 0);
+                        issue_pv_part(i, 0, v_desc, j > 0);
+                        FA_PROF(5)
                         ok = wait(p_full + 16 * i + 8, p_ph[i], 0x1238u + i);
-                        if (!ok) break;
+                        if (!ok) continue;
+                        FA_PROF(6 + i)
                         p_ph[i] ^= 1u;
                         tc_fence_after();
-                        issue_pv_half(i, 1, v_addr, true);
+                        issue_pv_part(i, 1, v_desc, true);
                         if (j + 1 < u.nblk[i]) {
                             if (!have_k) {
+                                FA_PROF(5)
                                 ok = wait(kv_full + 8 * s, ph, 0x1240u + s);
-                                if (!ok) break;
+                                if (!ok) continue;
+                                FA_PROF(1)
                                 tc_fence_after();
                                 k_addr = ring_smem + s * T::kTileBytes;
                                 k_slot = s;
@@ -329,6 +391,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     }
                 }
             }
+            FA_PROF(5)
+            FA_PROF_DUMP(0)
         }
     } else if (warp < 8) {
         setmaxnreg_dec<kWsRegsCorrection>();
@@ -336,257 +400,233 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         const int quad = warp & 3;                      // tensor-memory lane quadrant
         const int row_in_tile = quad * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-        uint32_t c_ph[2] = {0, 0};                      // corr_full
+        uint32_t x_ph[2] = {0, 0};                      // max_full: one completion per block of the tile
         uint32_t u_ph[2] = {0, 0};                      // sum_full / o_final: one completion per unit the tile takes part in
+        float m_run[2] = {-INFINITY, -INFINITY};        // the same running max the row's softmax threads keep
         bool ok = true;
-        // O_0 and O_1 start out free.
-        if (lane == 0 && first_unit < num_units) {
-            mbar_arrive(o_ready);
-            mbar_arrive(o_ready + 8);
+        FA_PROF_DECL
+        // One block of tile i: take the row maxima the softmax threads published, advance the
+        // running max, rescale O_i if it moved, and tell the MMA warp that O_i may be accumulated
+        // into.  Every block is acknowledged, the first of a unit included (there the arrival
+        // also says that the previous unit's epilogue has read O_i): the softmax warps can then
+        // never get two blocks ahead of this warp, which a one-bit barrier phase could not tell
+        // from none.
+        auto handle_block = [&](int i, bool first) {
+            FA_PROF(1)
+            ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 8 * i, x_ph[i] & 1u, 0x1500u + i));
+            if (!ok) return;
+            FA_PROF(0)
+            const uint32_t box = max_smem + (((x_ph[i] & 1u) * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
+            ++x_ph[i];
+            const float block_max = fmaxf(ld_shared_f32(box), ld_shared_f32(box + kTileQ * 4));
+            if (first) m_run[i] = -INFINITY;
+            const float alpha = advance_row_max(m_run[i], block_max, scale_log2);
+            if (!first && __any_sync(0xffffffffu, alpha != 1.f)) {
+                tc_fence_after();
+                const uint32_t t_o = tmem_base + lane_base + T::kColO + i * D;
+#pragma unroll 1
+                for (int c = 0; c < D / 16; ++c) {
+                    uint32_t o[16];
+                    tmem_ld_32x32b_x16(t_o + c * 16, o);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int x = 0; x < 16; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
+                    tmem_st_32x32b_x16(t_o + c * 16, o);
+                }
+                tmem_wait_st();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(o_ready + 8 * i);
+        };
+        if (first_unit < num_units) {
+            const UnitCoord u0 = unit_coord(first_unit, q_pairs, heads, seq_q, seq_k, causal);
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+                if (ok && u0.nblk[i] > 0) handle_block(i, true);
         }
         for (int id = first_unit; id < num_units && ok; id += unit_stride) {
             const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
+            // which tiles the CTA's next unit uses (its first block is acknowledged right after
+            // this unit's epilogue of the same tile)
+            bool next_has[2] = {false, false};
+            if (id + unit_stride < num_units) {
+                const UnitCoord un = unit_coord(id + unit_stride, q_pairs, heads, seq_q, seq_k, causal);
+                next_has[0] = un.nblk[0] > 0;
+                next_has[1] = un.nblk[1] > 0;
+            }
             for (int j = 1; j < u.nmax && ok; ++j) {
-                for (int i = 0; i < 2 && ok; ++i) {
-                    if (j >= u.nblk[i]) continue;
-                    ok = __all_sync(0xffffffffu, mbar_wait(guard, corr_full + 8 * i, c_ph[i], 0x1500u + i));
-                    if (!ok) break;
-                    c_ph[i] ^= 1u;
-                    const float alpha = alpha_ptr[i * kTileQ + row_in_tile];
-                    if (__any_sync(0xffffffffu, alpha != 1.f)) {
-                        tc_fence_after();
-                        const uint32_t t_o = tmem_base + lane_base + T::kColO + i * D;
-#pragma unroll 1
-                        for (int c = 0; c < D / 32; ++c) {
-                            uint32_t o[32];
-                            tmem_ld_32x32b_x32(t_o + c * 32, o);
-                            tmem_wait_ld();
 #pragma unroll
-                            for (int x = 0; x < 32; ++x) o[x] = __float_as_uint(__uint_as_float(o[x]) * alpha);
-                            tmem_st_32x32b_x32(t_o + c * 32, o);
-                        }
-                        tmem_wait_st();
-                        tc_fence_before();
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(o_ready + 8 * i);
+                for (int i = 0; i < 2; ++i) {
+                    if (!ok || j >= u.nblk[i]) continue;
+                    handle_block(i, false);
                 }
             }
             // ---------------------------------------------------------------------- epilogue
-            for (int i = 0; i < 2 && ok; ++i) {
-                if (u.nblk[i] == 0) continue;
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (!ok || u.nblk[i] == 0) continue;
+                FA_PROF(1)
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, sum_full + 8 * i, u_ph[i], 0x1510u + i));
-                if (!ok) break;
-                const float l = total_ptr[i * kTileQ + row_in_tile];
+                if (!ok) continue;
+                const uint32_t sums = sum_smem + (i * 2 * kTileQ + row_in_tile) * 4;
+                const float l = ld_shared_f32(sums) + ld_shared_f32(sums + kTileQ * 4);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sum_empty + 8 * i);
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, o_final + 8 * i, u_ph[i], 0x1518u + i));
-                if (!ok) break;
+                if (!ok) continue;
+                FA_PROF(2)
                 tc_fence_after();
                 const float inv = (l == 0.f) ? 1.f : (1.f / l);
                 const uint32_t t_o = tmem_base + lane_base + T::kColO + i * D;
-                // the stores of the previous tile have read the staging rows of this warp
-                if (lane == 0) tma_store_wait_read<0>();
-                __syncwarp();
+                const uint32_t row_addr = o_smem + row_in_tile * 128;
 #pragma unroll 1
-                for (int c = 0; c < D / 32; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32b_x32(t_o + c * 32, o);
+                for (int c = 0; c < D / 16; ++c) {
+                    uint32_t o[16];
+                    tmem_ld_32x32b_x16(t_o + c * 16, o);
                     tmem_wait_ld();
-                    if (c == D / 32 - 1) {
-                        // O_i is in registers: the next unit may overwrite it
-                        tc_fence_before();
+                    if ((c & 3) == 0) {
+                        // a new 64-column box: the stores issued so far have read this warp's staging rows
+                        if (lane == 0) tma_store_wait_read<0>();
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(o_ready + 8 * i);
                     }
-                    uint32_t h[16];
+                    uint32_t h[8];
 #pragma unroll
-                    for (int x = 0; x < 16; ++x)
+                    for (int x = 0; x < 8; ++x)
                         h[x] = pack_f16x2(__uint_as_float(o[2 * x]) * inv, __uint_as_float(o[2 * x + 1]) * inv);
-                    const uint32_t row_addr = o_smem + (c >> 1) * kBoxBytes + row_in_tile * 128;
-#pragma unroll
-                    for (int jj = 0; jj < 4; ++jj) {
-                        const int chunk = (c & 1) * 4 + jj;
-                        st_shared_v4(row_addr + ((chunk ^ (row_in_tile & 7)) << 4), h[4 * jj], h[4 * jj + 1],
-                                     h[4 * jj + 2], h[4 * jj + 3]);
+                    const int chunk = (c & 3) * 2;       // 16-byte chunks of the 128-byte staging row
+                    st_shared_v4(row_addr + ((chunk ^ (row_in_tile & 7)) << 4), h[0], h[1], h[2], h[3]);
+                    st_shared_v4(row_addr + (((chunk + 1) ^ (row_in_tile & 7)) << 4), h[4], h[5], h[6], h[7]);
+                    if ((c & 3) == 3) {
+                        // the box is complete: this warp's 32 rows of it, to every destination
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            for (int d = 0; d < n_dst; ++d)
+                                tma_store_4d(&tmap_o.m[d], o_smem + quad * 32 * 128, (c >> 2) * 64,
+                                             u.q0 + i * kTileQ + quad * 32, u.head, u.batch);
+                            tma_store_commit();
+                        }
                     }
-                }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) {
-                    // this warp's 32 rows of every 64-column box, to every destination
-                    for (int d = 0; d < n_dst; ++d)
-                        for (int b = 0; b < T::kBoxes; ++b)
-                            tma_store_4d(&tmap_o.m[d], o_smem + b * kBoxBytes + quad * 32 * 128, b * 64,
-                                         u.q0 + i * kTileQ + quad * 32, u.head, u.batch);
-                    tma_store_commit();
                 }
                 u_ph[i] ^= 1u;
+                FA_PROF(3)
+                // O_i has been read: first block of the CTA's next unit, if this tile has one
+                if (next_has[i]) handle_block(i, true);
             }
         }
         if (lane == 0) tma_store_wait_all<0>();
+        if (warp == 4) FA_PROF_DUMP(24)
     } else {
         setmaxnreg_inc<kWsRegsSoftmax>();
         // ------------------------------------------------------------------ softmax warps
         const int i = (warp - 8) >> 3;                  // query tile of this warp
         const int quad = warp & 3;                      // tensor-memory lane quadrant
-        const int half = ((warp - 8) >> 2) & 1;         // which 16 lanes of the quadrant
-        const int qt = lane & 3;                        // position in the quad: columns 2qt, 2qt+1 of every 8
-        const int row_a = quad * 32 + half * 16 + (lane >> 2);   // rows of this thread inside the tile
-        const int row_b = row_a + 8;
-        const uint32_t t_s = tmem_base + (static_cast<uint32_t>(quad * 32 + half * 16) << 16) + T::kColS + i * kTileKV;
+        const int half = ((warp - 8) >> 2) & 1;         // which 64 keys of the block
+        const int row_in_tile = quad * 32 + lane;
+        const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + T::kColS + i * kTileKV;
+        const uint32_t t_s = t_row + half * 64;         // this thread's scores
+        const uint32_t t_p = t_row + half * 32;         // where its P goes (packed pairs)
         const Exp2PolyConsts poly = make_exp2_poly_consts();
         const f32x2 scale2 = pack2(scale_log2, scale_log2);
-        uint32_t s_ph = 0;
+        uint32_t blocks_done = 0;                       // parity of s_full / max_full and of the maxima slot
         uint32_t units_done = 0;
         bool ok = true;
+        FA_PROF_DECL
         for (int id = first_unit; id < num_units && ok; id += unit_stride) {
             const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
-            const int n = u.nblk[i];
+            const int n = i ? u.nblk[1] : u.nblk[0];
             if (n == 0) continue;
-            const int grow_a = u.q0 + i * kTileQ + row_a;   // query index of row a in the sequence
-            float m_a = -INFINITY, m_b = -INFINITY;         // running max the accumulators are scaled to
-            f32x2 l_a = pack2(0.f, 0.f), l_b = pack2(0.f, 0.f);   // partial row sums (this thread's columns)
+            const int grow = u.q0 + i * kTileQ + row_in_tile;   // query index of this row in the sequence
+            float m = -INFINITY;                        // running max the accumulators are scaled to
+            f32x2 l = pack2(0.f, 0.f);                  // partial row sum (this thread's keys)
             for (int j = 0; j < n && ok; ++j) {
-                ok = __all_sync(0xffffffffu, mbar_wait(guard, s_full + 8 * i, s_ph, 0x1300u + i));
+                FA_PROF(4)
+                const uint32_t par = blocks_done & 1u;
+                ok = __all_sync(0xffffffffu, mbar_wait(guard, s_full + 8 * i, par, 0x1300u + i));
                 if (!ok) break;
-                s_ph ^= 1u;
+                FA_PROF(0)
                 tc_fence_after();
-                const int col0 = j * kTileKV;
-                const bool need_mask =
-                    (col0 + kTileKV > seq_k) || (causal && (col0 + kTileKV - 1 > u.q0 + i * kTileQ));
-                const int lim_a = causal ? min(seq_k - 1, grow_a) : (seq_k - 1);   // last visible key
-                const int lim_b = causal ? min(seq_k - 1, grow_a + 8) : (seq_k - 1);
-                // ------------------------------------------------ pass 1: row max
-                float mx_a = -INFINITY, mx_b = -INFINITY;
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_16x256b_x8(t_s + c * 64, v);
-                    tmem_wait_ld();
-                    if (need_mask) {
+                uint32_t sa[32], sb[32];
+                tmem_ld_32x32b_x32(t_s, sa);
+                tmem_ld_32x32b_x32(t_s + 32, sb);
+                tmem_wait_ld();
+                const int col0 = j * kTileKV + half * 64;
+                if ((col0 + 64 > seq_k) || (causal && (col0 + 63 > u.q0 + i * kTileQ))) {
+                    const int limit = causal ? min(seq_k - 1, grow) : (seq_k - 1);  // last visible key
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const int col = col0 + c * 64 + 8 * k + 2 * qt;
-                            if (col > lim_a) v[4 * k] = 0xff800000u;
-                            if (col + 1 > lim_a) v[4 * k + 1] = 0xff800000u;
-                            if (col > lim_b) v[4 * k + 2] = 0xff800000u;
-                            if (col + 1 > lim_b) v[4 * k + 3] = 0xff800000u;
-                        }
-                    }
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-                        mx_a = max3(mx_a, __uint_as_float(v[4 * k]), __uint_as_float(v[4 * k + 1]));
-                        mx_b = max3(mx_b, __uint_as_float(v[4 * k + 2]), __uint_as_float(v[4 * k + 3]));
+                    for (int x = 0; x < 32; ++x) {
+                        if (col0 + x > limit) sa[x] = 0xff800000u;  // -inf
+                        if (col0 + 32 + x > limit) sb[x] = 0xff800000u;
                     }
                 }
-                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
-                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
-                mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
-                mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-                // Rescale only when the max moved enough to matter (always on the first block).
-                const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
-                const bool need_a = (mn_a - m_a) * scale_log2 > kRescaleLog2 || m_a == -INFINITY;
-                const bool need_b = (mn_b - m_b) * scale_log2 > kRescaleLog2 || m_b == -INFINITY;
-                float alpha_a = 1.f, alpha_b = 1.f;
-                if (__any_sync(0xffffffffu, need_a || need_b)) {
-                    if (need_a) {
-                        alpha_a = (m_a == -INFINITY) ? 0.f : fast_exp2((m_a - mn_a) * scale_log2);
-                        m_a = mn_a;
-                        l_a = mul2(l_a, pack2(alpha_a, alpha_a));
-                    }
-                    if (need_b) {
-                        alpha_b = (m_b == -INFINITY) ? 0.f : fast_exp2((m_b - mn_b) * scale_log2);
-                        m_b = mn_b;
-                        l_b = mul2(l_b, pack2(alpha_b, alpha_b));
-                    }
-                }
-                if (j > 0) {
-                    // publish the factors of this block for the correction warpgroup
-                    if (qt == 0) {
-                        alpha_ptr[i * kTileQ + row_a] = alpha_a;
-                        alpha_ptr[i * kTileQ + row_b] = alpha_b;
-                    }
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(corr_full + 8 * i);
-                }
-                // ------------------------------------------------ pass 2: P = exp2(s*scale - m*scale)
-                const float nm_a = -((m_a == -INFINITY) ? 0.f : m_a) * scale_log2;
-                const float nm_b = -((m_b == -INFINITY) ? 0.f : m_b) * scale_log2;
-                const f32x2 nm2_a = pack2(nm_a, nm_a), nm2_b = pack2(nm_b, nm_b);
-#pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_16x256b_x8(t_s + c * 64, v);
-                    tmem_wait_ld();
-                    if (need_mask) {
+                // four independent chains
+                float mc[4];
 #pragma unroll
-                        for (int k = 0; k < 8; ++k) {
-                            const int col = col0 + c * 64 + 8 * k + 2 * qt;
-                            if (col > lim_a) v[4 * k] = 0xff800000u;
-                            if (col + 1 > lim_a) v[4 * k + 1] = 0xff800000u;
-                            if (col > lim_b) v[4 * k + 2] = 0xff800000u;
-                            if (col + 1 > lim_b) v[4 * k + 3] = 0xff800000u;
-                        }
-                    }
-                    uint32_t pr[16];
+                for (int c = 0; c < 4; ++c) {
+                    const uint32_t* s = (c < 2 ? sa : sb) + (c & 1) * 16;
+                    mc[c] = max3(__uint_as_float(s[0]), __uint_as_float(s[1]), __uint_as_float(s[2]));
 #pragma unroll
-                    for (int k = 0; k < 8; ++k) {
-#pragma unroll
-                        for (int r = 0; r < 2; ++r) {
-                            const f32x2 xs = fma2(pack2(__uint_as_float(v[4 * k + 2 * r]), __uint_as_float(v[4 * k + 2 * r + 1])),
-                                                  scale2, r ? nm2_b : nm2_a);
-                            f32x2 pp;
-                            // EMU of every 4 pairs take the polynomial path, the rest the SFU.
-                            if (((2 * k + r) & 3) < EMU) {
-                                pp = exp2_poly2(xs, poly);
-                            } else {
-                                float x0, x1;
-                                unpack2(xs, x0, x1);
-                                pp = pack2(fast_exp2(x0), fast_exp2(x1));
-                            }
-                            if (r) l_b = add2(l_b, pp); else l_a = add2(l_a, pp);
-                            float p0, p1;
-                            unpack2(pp, p0, p1);
-                            pr[2 * k + r] = pack_f16x2(p0, p1);
-                        }
-                    }
-                    // 64 keys = 32 packed columns; the scores they replace are already consumed.
-                    tmem_st_16x128b_x8(t_s + c * 32, pr);
-                    tmem_wait_st();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(p_full + 16 * i + 8 * c);
+                    for (int x = 3; x < 15; x += 2) mc[c] = max3(mc[c], __uint_as_float(s[x]), __uint_as_float(s[x + 1]));
+                    mc[c] = fmaxf(mc[c], __uint_as_float(s[15]));
                 }
+                const float mine = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
+                // exchange with the thread that holds the other 64 keys of this row
+                const uint32_t box = max_smem + ((par * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
+                st_shared_f32(box + half * kTileQ * 4, mine);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(max_full + 8 * i);
+                ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 8 * i, par, 0x1308u + i));
+                if (!ok) break;
+                const float theirs = ld_shared_f32(box + (half ^ 1) * kTileQ * 4);
+                // fmaxf in the order the correction thread uses (half 0, half 1)
+                const float block_max = half ? fmaxf(theirs, mine) : fmaxf(mine, theirs);
+                const float alpha = advance_row_max(m, block_max, scale_log2);
+                l = mul2(l, pack2(alpha, alpha));
+                ++blocks_done;
+                FA_PROF(1)
+                const float nm = -((m == -INFINITY) ? 0.f : m) * scale_log2;
+                const f32x2 nm2 = pack2(nm, nm);
+                uint32_t pr[8];
+                exp_16<EMU>(sa, pr, scale2, nm2, l, poly);
+                tmem_st_32x32b_x8(t_p, pr);              // keys 0..15 of this half -> 8 packed columns
+                exp_16<EMU>(sa + 16, pr, scale2, nm2, l, poly);
+                tmem_st_32x32b_x8(t_p + 8, pr);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full + 16 * i);          // first 32 keys of both halves
+                FA_PROF(2)
+                exp_16<EMU>(sb, pr, scale2, nm2, l, poly);
+                tmem_st_32x32b_x8(t_p + 16, pr);
+                exp_16<EMU>(sb + 16, pr, scale2, nm2, l, poly);
+                tmem_st_32x32b_x8(t_p + 24, pr);
+                tmem_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full + 16 * i + 8);      // the rest
+                FA_PROF(3)
             }
             if (!ok) break;
             // ------------------------------------------------ row sums of the finished unit
-            float ta, tb, hi;
-            unpack2(l_a, ta, hi);
-            ta += hi;
-            unpack2(l_b, tb, hi);
-            tb += hi;
-            ta += __shfl_xor_sync(0xffffffffu, ta, 1);
-            tb += __shfl_xor_sync(0xffffffffu, tb, 1);
-            ta += __shfl_xor_sync(0xffffffffu, ta, 2);
-            tb += __shfl_xor_sync(0xffffffffu, tb, 2);
+            float t0, t1;
+            unpack2(l, t0, t1);
             if (units_done > 0) {
                 // the correction warps have taken the previous unit's sums
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, sum_empty + 8 * i, (units_done - 1) & 1u, 0x1310u + i));
                 if (!ok) break;
             }
-            if (qt == 0) {
-                total_ptr[i * kTileQ + row_a] = ta;
-                total_ptr[i * kTileQ + row_b] = tb;
-            }
+            st_shared_f32(sum_smem + ((i * 2 + half) * kTileQ + row_in_tile) * 4, t0 + t1);
             __syncwarp();
             if (lane == 0) mbar_arrive(sum_full + 8 * i);
             ++units_done;
         }
+        if (warp == 8) FA_PROF_DUMP(8)
+        if (warp == 16) FA_PROF_DUMP(16)
     }
 
     // --------------------------------------------------------------------------- teardown
-    if (*abort_ptr != 0) {
+    if (ld_shared_u32(abort_slot) != 0) {
         for (int it = 0; it < 64; ++it) __nanosleep(100000);
     }
     tc_fence_before();

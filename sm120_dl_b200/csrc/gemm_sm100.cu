@@ -564,13 +564,8 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
 
     // Set once per (kernel, device); the reference sets it on every call
     // (gemm/gemm_cute.hpp:339-341).
-    static bool attr_done[64] = {};
-    if (!attr_done[dev->device]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
-        if (e != cudaSuccess) return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", cfg.name,
-                                          T::kSmemBytes, cudaGetErrorString(e));
-        attr_done[dev->device] = true;
-    }
+    static bool attr_done[kMaxDevices] = {};
+    if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
 
     const int num_tiles = ((M + kCtaM * CTA_GROUP - 1) / (kCtaM * CTA_GROUP)) * ((N + BN - 1) / BN);
     int groups = dev->sm_count / CTA_GROUP;
@@ -625,13 +620,8 @@ int launch_gemm_splitk(const DeviceInfo* dev, const b200_gemm_config& cfg, int M
         c_list.p[d] = C_list[d];
     }
 
-    static bool attr_done[64] = {};
-    if (!attr_done[dev->device]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T::kSmemBytes);
-        if (e != cudaSuccess) return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", cfg.name,
-                                          T::kSmemBytes, cudaGetErrorString(e));
-        attr_done[dev->device] = true;
-    }
+    static bool attr_done[kMaxDevices] = {};
+    if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
     const long tiles = static_cast<long>((M + kCtaM - 1) / kCtaM) * ((N + BN - 1) / BN);
     if (tiles * split > 0x7fffffffL) return fail(B200_ESHAPE, "%s: too many tiles", cfg.name);
 
@@ -656,7 +646,7 @@ int launch_gemm_splitk(const DeviceInfo* dev, const b200_gemm_config& cfg, int M
 // Clusters of `split` CTAs of this kernel the current device can hold at once (a cluster must
 // fit inside one GPC, so 8-CTA clusters leave SMs unused), or 0 when it cannot be asked.
 template <int BN, int STAGES>
-int splitk_active_clusters(int split) {
+int splitk_active_clusters(int split, int sm_count) {
     using T = SplitKTraits<BN, STAGES>;
     static int cached[9] = {};
     if (split < 1 || split > 8) return 0;
@@ -664,7 +654,7 @@ int splitk_active_clusters(int split) {
     auto kernel = gemm_splitk_kernel<BN, STAGES>;
     int n = 0;
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(static_cast<unsigned>(split * 148), 1, 1);
+    lc.gridDim = dim3(static_cast<unsigned>(split * sm_count), 1, 1);
     lc.blockDim = dim3(kThreads, 1, 1);
     lc.dynamicSmemBytes = T::kSmemBytes;
     cudaLaunchAttribute attr[1];
@@ -684,7 +674,7 @@ int splitk_active_clusters(int split) {
     return n;
 }
 
-using ClustersFn = int (*)(int);
+using ClustersFn = int (*)(int, int);
 
 struct Entry {
     b200_gemm_config cfg;
@@ -795,23 +785,27 @@ int b200_gemm_default_config(int M, int N, int K) {
     // epilogue (12 us for 8-CTA clusters), and its waves are counted in clusters the device
     // can hold at once.  Work on a ragged edge is paid like any other.
     if (M <= 0 || N <= 0 || K <= 0) return -1;
+    // SMs of the current device; without a usable device (host-side planning) a B200's 148.
+    int sms = b200::current_sm_count();
+    if (sms <= 0) sms = 148;
     int best = -1;
     double best_cost = 0.0;
     for (int i = 0; i < b200::kNumEntries; ++i) {
         const b200_gemm_config& c = b200::kEntries[i].cfg;
         const long tiles = static_cast<long>((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
         const long kb = (K + c.bk - 1) / c.bk;
-        if (c.split_k > 1 && (tiles >= 148 || kb / c.split_k < 16)) continue;  // see b200dl.h
-        long slots = 148 / c.cta_group;   // CTA pairs or CTAs resident at once
+        if (c.split_k > 1 && (tiles >= sms || kb / c.split_k < 16)) continue;  // see b200dl.h
+        long slots = sms / c.cta_group;   // CTA pairs or CTAs resident at once
         if (c.split_k > 1) {
-            const int held = b200::kEntries[i].active_clusters(c.split_k);
-            slots = held > 0 ? held : (c.split_k == 8 ? 14 : 144 / c.split_k);
+            const int held = b200::kEntries[i].active_clusters(c.split_k, sms);
+            // a cluster must fit inside one GPC, so large clusters leave SMs unused
+            slots = held > 0 ? held : (c.split_k == 8 ? sms / 10 : (sms - 4) / c.split_k);
         }
         const long waves = (tiles + slots - 1) / slots;
         const long ctas = tiles * c.cta_group * c.split_k;
-        const long active = ctas < 148 ? ctas : 148;
+        const long active = ctas < sms ? ctas : sms;
         double t_kb = c.bn >= 256 ? (c.cta_group == 2 ? 0.40 : 0.43) : c.bn >= 192 ? 0.36 : c.bn >= 128 ? 0.29 : 0.22;
-        if (ctas < 148 || c.split_k > 1) {
+        if (ctas < sms || c.split_k > 1) {
             const double bytes = (128.0 + c.bn / c.cta_group) * 128.0;                 // A and B rows of one k-block
             const double gbs = 95.0 < 11500.0 / active ? 95.0 : 11500.0 / active;       // per CTA
             const double t_mem = bytes / (gbs * 1e3);
@@ -822,7 +816,7 @@ int b200_gemm_default_config(int M, int N, int K) {
         const double fixed = c.split_k > 1 ? (c.split_k == 8 ? 12.0 : 8.0 + 0.25 * c.split_k)
                                            : (c.acc_bufs > 1 ? 4.0 : 4.0 + 1.5 * (waves - 1)) +
                                                  // the pair handshake per tile shows on latency-bound problems
-                                                 ((c.cta_group == 2 && tiles < 74) ? 1.0 : 0.0);
+                                                 ((c.cta_group == 2 && tiles < sms / 2) ? 1.0 : 0.0);
         double cost = waves * kb_per_cta * t_kb + fixed;
         // ties: deeper ring, strip width 8 (fastest measured on 8192^3)
         cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == 8 ? 0.0002 : 0.0);
@@ -834,101 +828,101 @@ int b200_gemm_default_config(int M, int N, int K) {
     return best;
 }
 
+}  // extern "C"
+
+namespace b200 {
+namespace {
+
+// Argument checks shared by every GEMM entry point.  On success *entry is the config's table
+// entry; the device-dependent check (shared memory) is done by the caller, which knows
+// which device record it uses.
+int check_gemm_args(int config, int M, int N, int K, const void* A, int64_t lda, const void* B, int64_t ldb,
+                    void* const* C_list, int n_dst, int64_t ldc, const Entry** entry) {
+    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
+    if (A == nullptr || B == nullptr || C_list == nullptr) return fail(B200_EINVAL, "null matrix pointer");
+    if (n_dst < 1 || n_dst > kMaxDst) return fail(B200_EINVAL, "n_dst must be 1..%d (got %d)", kMaxDst, n_dst);
+    for (int d = 0; d < n_dst; ++d)
+        if (C_list[d] == nullptr) return fail(B200_EINVAL, n_dst == 1 ? "null matrix pointer" : "destination %d is null", d);
+    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
+    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
+    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
+        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
+                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
+    }
+    *entry = &kEntries[config];
+    return B200_OK;
+}
+
+int run_gemm(const DeviceInfo* dev, const Entry& e, int M, int N, int K, const void* A, int64_t lda, const void* B,
+             int64_t ldb, void* const* C_list, int n_dst, int64_t ldc, bool is_bf16, void* stream) {
+    if (dev == nullptr) return B200_ENODEVICE;
+    if (e.cfg.smem_bytes > dev->max_smem_optin) {
+        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
+                    dev->max_smem_optin);
+    }
+    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, is_bf16, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+}  // namespace b200
+
+extern "C" {
+
 int b200_gemm_bf16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                       int64_t ldb, void* C, int64_t ldc, void* stream) {
     using namespace b200;
-    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
-    const Entry& e = kEntries[config];
-    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
-    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
-    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
-        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
-                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
-    }
-    const DeviceInfo* dev = current_device();
-    if (dev == nullptr) return B200_ENODEVICE;
-    if (e.cfg.smem_bytes > dev->max_smem_optin) {
-        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
-                    dev->max_smem_optin);
-    }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, static_cast<cudaStream_t>(stream));
+    const Entry* e = nullptr;
+    if (int rc = check_gemm_args(config, M, N, K, A, lda, B, ldb, &C, 1, ldc, &e)) return rc;
+    return run_gemm(current_device(), *e, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, stream);
 }
 
 int b200_gemm_f16_tn(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
-                      int64_t ldb, void* C, int64_t ldc, void* stream) {
+                     int64_t ldb, void* C, int64_t ldc, void* stream) {
     using namespace b200;
-    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
-    const Entry& e = kEntries[config];
-    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
-    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
-    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
-        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
-                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
-    }
-    const DeviceInfo* dev = current_device();
-    if (dev == nullptr) return B200_ENODEVICE;
-    if (e.cfg.smem_bytes > dev->max_smem_optin) {
-        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
-                    dev->max_smem_optin);
-    }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, false, static_cast<cudaStream_t>(stream));
+    const Entry* e = nullptr;
+    if (int rc = check_gemm_args(config, M, N, K, A, lda, B, ldb, &C, 1, ldc, &e)) return rc;
+    return run_gemm(current_device(), *e, M, N, K, A, lda, B, ldb, &C, 1, ldc, false, stream);
 }
 
 int b200_gemm_bf16_tn_scatter(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                               int64_t ldb, void* const* C_list, int n_dst, int64_t ldc, void* stream) {
     using namespace b200;
-    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
-    const Entry& e = kEntries[config];
-    if (A == nullptr || B == nullptr || C_list == nullptr) return fail(B200_EINVAL, "null matrix pointer");
-    if (n_dst < 1 || n_dst > kMaxDst) return fail(B200_EINVAL, "n_dst must be 1..%d (got %d)", kMaxDst, n_dst);
-    for (int d = 0; d < n_dst; ++d)
-        if (C_list[d] == nullptr) return fail(B200_EINVAL, "destination %d is null", d);
-    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
-    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
-        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
-                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
-    }
-    const DeviceInfo* dev = current_device();
-    if (dev == nullptr) return B200_ENODEVICE;
-    if (e.cfg.smem_bytes > dev->max_smem_optin) {
-        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
-                    dev->max_smem_optin);
-    }
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, true, static_cast<cudaStream_t>(stream));
+    const Entry* e = nullptr;
+    if (int rc = check_gemm_args(config, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, &e)) return rc;
+    return run_gemm(current_device(), *e, M, N, K, A, lda, B, ldb, C_list, n_dst, ldc, true, stream);
 }
 
 int b200_gemm_bf16_tn_noalloc(int config, int M, int N, int K, const void* A, int64_t lda, const void* B,
                               int64_t ldb, void* C, int64_t ldc, void* stream) {
     using namespace b200;
-    if (config < 0 || config >= kNumEntries) return fail(B200_EINVAL, "unknown GEMM config index %d", config);
-    const Entry& e = kEntries[config];
-    if (A == nullptr || B == nullptr || C == nullptr) return fail(B200_EINVAL, "null matrix pointer");
-    if (M <= 0 || N <= 0 || K <= 0) return fail(B200_ESHAPE, "M, N, K must be positive (got %d %d %d)", M, N, K);
-    if (N % 8 != 0) return fail(B200_ESHAPE, "N must be a multiple of 8 (TMA stores clip at 16-byte granularity), got %d", N);
-    if (lda < K || ldb < K || ldc < N || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) {
-        return fail(B200_EINVAL, "leading dimensions must be >= the row length and multiples of 8 (lda %lld ldb %lld ldc %lld)",
-                    static_cast<long long>(lda), static_cast<long long>(ldb), static_cast<long long>(ldc));
-    }
+    const Entry* e = nullptr;
+    if (int rc = check_gemm_args(config, M, N, K, A, lda, B, ldb, &C, 1, ldc, &e)) return rc;
     // Scratch this launch needs against what the built-in array can serve.
     const size_t scratch_needed = kStatusBlockBytes;
     if (scratch_needed > kNoAllocScratchBytes) {
         return fail(B200_ESHAPE, "%s on %dx%dx%d needs %zu bytes of scratch; the allocation-free entry point serves at most %zu",
-                    e.cfg.name, M, N, K, scratch_needed, kNoAllocScratchBytes);
+                    e->cfg.name, M, N, K, scratch_needed, kNoAllocScratchBytes);
     }
     const DeviceInfo* dev = noalloc_device();
     if (dev == nullptr) return B200_ENODEVICE;
-    if (e.cfg.smem_bytes > dev->max_smem_optin) {
-        return fail(B200_ESHAPE, "%s needs %d bytes of shared memory, device allows %d", e.cfg.name, e.cfg.smem_bytes,
-                    dev->max_smem_optin);
-    }
     // The array keeps whatever the previous call left; the status word must start at zero
     // for this launch's record.  Ordered on the caller's stream, ahead of the kernel.
     cudaError_t ce = cudaMemsetAsync(dev->status, 0, kStatusBlockBytes, static_cast<cudaStream_t>(stream));
     if (ce != cudaSuccess) return fail(B200_ECUDA, "clearing the scratch block failed: %s", cudaGetErrorString(ce));
-    return e.launch(dev, e.cfg, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, static_cast<cudaStream_t>(stream));
+    return run_gemm(dev, *e, M, N, K, A, lda, B, ldb, &C, 1, ldc, true, stream);
+}
+
+int b200_gemm_noalloc_status(uint32_t* code) {
+    using namespace b200;
+    if (code == nullptr) return fail(B200_EINVAL, "code is null");
+    const DeviceInfo* dev = noalloc_device();
+    if (dev == nullptr) return B200_ENODEVICE;
+    // Plain synchronise + 4-byte copy from the array's resolved address: nothing is allocated.
+    cudaError_t ce = cudaDeviceSynchronize();
+    if (ce != cudaSuccess) return fail(B200_ECUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(ce));
+    ce = cudaMemcpy(code, dev->status, sizeof(uint32_t), cudaMemcpyDeviceToHost);
+    if (ce != cudaSuccess) return fail(B200_ECUDA, "reading the scratch block's status word: %s", cudaGetErrorString(ce));
+    return B200_OK;
 }
 
 }  // extern "C"

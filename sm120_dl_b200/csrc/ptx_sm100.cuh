@@ -123,6 +123,49 @@ __device__ __forceinline__ bool mbar_wait(const WaitGuard& g, uint32_t bar, uint
     return mbar_wait_slow(g, bar, parity, site);
 }
 
+// The same guard with the abort flag held as a 32-bit shared-memory address (two registers
+// fewer in every role that waits; the attention kernel's softmax warps are register-bound).
+__device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.volatile.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_shared_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.volatile.shared::cta.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ float ld_shared_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.volatile.shared::cta.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_shared_f32(uint32_t addr, float v) {
+    asm volatile("st.volatile.shared::cta.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+struct WaitGuardS {
+    uint32_t abort_addr;            // shared::cta address of the CTA's abort word
+    uint32_t* status;               // global memory, one word per device (0 = healthy)
+};
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t abort_addr, uint32_t* status, uint32_t bar, uint32_t parity,
+                                            uint32_t site) {
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 0xffu) == 0) {
+            if (ld_shared_u32(abort_addr) != 0) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                st_shared_u32(abort_addr, 1);
+                atomicCAS(status, 0u, 0x80000000u | site);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ bool mbar_wait(const WaitGuardS& g, uint32_t bar, uint32_t parity, uint32_t site) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(g.abort_addr, g.status, bar, parity, site);
+}
+
 // --------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -354,6 +397,12 @@ __device__ __forceinline__ void tmem_st_32x32b_x16(uint32_t taddr, const uint32_
         "r"(r[14]), "r"(r[15])
         : "memory");
 }
+__device__ __forceinline__ void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+        : "memory");
+}
 // TMEM -> registers, 16 lanes x 256 bits per repetition, 8 repetitions (64 columns): the warp
 // reads lanes [L, L+16) where L is the lane field of taddr (the warp's quadrant base, or that
 // plus 16).  Thread t holds, for repetition k (columns 8k..8k+7): r[4k] and r[4k+1] = lane
@@ -376,6 +425,21 @@ __device__ __forceinline__ void tmem_st_16x128b_x8(uint32_t taddr, const uint32_
         "tcgen05.st.sync.aligned.16x128b.x8.b32 [%0], "
         "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// Four repetitions of the two shapes above: 32 columns (16 registers) and 16 columns (8).
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.16x128b.x4.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
         : "memory");
 }
 __device__ __forceinline__ void tmem_wait_ld() {

@@ -12,7 +12,6 @@ namespace {
 
 thread_local char t_error[512] = "";
 
-constexpr int kMaxDevices = 64;
 DeviceInfo g_devices[kMaxDevices];
 bool g_device_ready[kMaxDevices] = {};
 std::mutex g_mutex;
@@ -67,6 +66,28 @@ const DeviceInfo* current_device() {
     g_devices[dev] = info;
     g_device_ready[dev] = true;
     return &g_devices[dev];
+}
+
+int current_sm_count() {
+    int dev = -1, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
+int set_smem_attribute_once(const void* kernel, int smem_bytes, int device, bool* done, const char* name) {
+    static std::mutex mu;
+    if (device < 0 || device >= kMaxDevices) return fail(B200_ENODEVICE, "device index %d out of range", device);
+    std::lock_guard<std::mutex> lock(mu);
+    if (done[device]) return B200_OK;
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess)
+        return fail(B200_ECUDA, "cudaFuncSetAttribute(%s, smem %d): %s", name, smem_bytes, cudaGetErrorString(e));
+    done[device] = true;
+    return B200_OK;
 }
 
 int encode_tmap_2byte(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,

@@ -27,6 +27,19 @@ struct DeviceInfo {
 // message on failure.
 const DeviceInfo* current_device();
 
+constexpr int kMaxDevices = 64;
+
+// SM count of the current device, or 0 when there is none; allocates nothing.
+int current_sm_count();
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize, set once per (kernel, device); `done` is the
+// caller's per-kernel table.  Safe to call from several host threads.
+int set_smem_attribute_once(const void* kernel, int smem_bytes, int device, bool* done, const char* name);
+template <typename Kernel>
+int set_smem_once(Kernel kernel, int smem_bytes, int device, bool (&done)[kMaxDevices], const char* name) {
+    return set_smem_attribute_once(reinterpret_cast<const void*>(kernel), smem_bytes, device, done, name);
+}
+
 // Encodes a tiled tensor map for 2-byte elements.  dims/strides are innermost-first;
 // strides_bytes[i] is the byte stride of dimension i+1 (dimension 0 is contiguous).
 // Returns 0 or a negative B200_E* code.

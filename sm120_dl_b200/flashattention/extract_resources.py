@@ -8,7 +8,7 @@ of libb200dl.so.  The log is what `python -m sm120_dl_b200.build lib --force --p
 prints (and stores as sm120_dl_b200/build/build.log).  Mangled kernel names are mapped back
 to config names:
 
-    fa_fwd_ws_kernel<D, STAGES, EMU>                  -> hd{D}_..._s{STAGES}_e{EMU}_r4
+    fa_fwd_ws_kernel<D, STAGES, EMU>                  -> hd{D}_..._s{STAGES}_e{EMU}_r2
     fa_fwd_kernel<D, STAGES, EMU>                     -> hd{D}_..._s{STAGES}_e{EMU}_r1
     gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC>   -> bf16_bm{128*CTA_GROUP}_bn{BN}_bk64_s{STAGES}_cta{..}_acc{..}
                                                          (the raster width is a launch argument)
@@ -42,7 +42,7 @@ def kernel_label(mangled):
         finally:
             sys.path.remove(HERE)
         head_dim, stages, emu = (int(x) for x in m.groups()[1:])
-        return flash_configs.config_name(head_dim, stages, emu, 4 if m.group(1) else 1)
+        return flash_configs.config_name(head_dim, stages, emu, 2 if m.group(1) else 1)
     m = GEMM_ARGS.search(mangled)
     if m:
         bn, stages, cta_group, acc = (int(x) for x in m.groups())

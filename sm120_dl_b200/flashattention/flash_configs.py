@@ -13,9 +13,9 @@ with Blackwell's vocabulary instead of mma.sync warp grids:
   stages     ring slots shared by K and V blocks (K_0, V_0, K_1, V_1, ...)
   layout     how the softmax is laid over threads (the reference ships two warp layouts too,
              v3_mMnNkN and v3_mMn1k1):
-               r4  four threads per query row (16 softmax warps), a correction warpgroup that
-                   rescales O and writes the output, persistent CTAs; one more shared-memory
-                   tile (output staging) and 24 warps
+               r2  two threads per query row (16 softmax warps), a correction warpgroup that
+                   rescales O and writes the output, persistent CTAs; a 16 KiB staging box
+                   for the output and 24 warps
                r1  one thread per query row (8 softmax warps) that also rescales O; one CTA
                    per 256 query rows, 12 warps
   emu        quarters of the exponentials evaluated by a polynomial on the FMA pipe
@@ -36,12 +36,12 @@ TILE_Q = 128
 Q_TILES = 2
 TILE_KV = 128
 SEQ_GRANULARITY = 64
-LAYOUTS = (1, 4)                                     # first = default
-STAGE_VALUES = {(64, 4): (8, 4), (128, 4): (4,), (64, 1): (8, 4), (128, 1): (5, 3)}
+LAYOUTS = (1, 2)                                     # first = default
+STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3)}
 # Quarters of the exponentials evaluated by a polynomial on the FMA pipe instead of the SFU
 # (the SFU's 16 ex2 per clock are the co-bottleneck at head_dim 128, the bottleneck at 64).
 EMU_VALUES = {64: (1, 0, 2), 128: (0, 1, 2)}   # first = default (fastest measured)
-NUM_WARPS = {4: 24, 1: 12}
+NUM_WARPS = {2: 24, 1: 12}
 DEFAULT_MAX_SMEM_KB = 227
 SMEM_LIMIT = DEFAULT_MAX_SMEM_KB * 1024
 TMEM_COLUMNS = 512
@@ -52,12 +52,13 @@ def tile_bytes(head_dim):
 
 
 def smem_bytes(head_dim, stages, layout):
-    if layout == 4:
-        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], corr_full[2], o_ready[2],
-        # o_final[2], sum_full[2], sum_empty[2]; two [2][128] fp32 arrays; one staging tile
+    if layout == 2:
+        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2], o_ready[2],
+        # o_final[2], sum_full[2], sum_empty[2]; row maxima [2][2][2][128] and row sums
+        # [2][2][128] in fp32; one 128 x 64 staging box for the output
         barriers = (2 + 2 * stages + 2 + 4 + 2 + 2 + 2 + 2 + 2) * 8 + 16
-        needed = (Q_TILES + stages + 1) * tile_bytes(head_dim) + 2 * 2 * TILE_Q * 4 + barriers
-        return min(needed + 1024, SMEM_LIMIT) if needed <= SMEM_LIMIT else needed
+        small = 2 * 2 * 2 * TILE_Q * 4 + 2 * 2 * TILE_Q * 4 + barriers
+        return (Q_TILES + stages) * tile_bytes(head_dim) + 128 * 128 + small + 1024
     barriers = (1 + 2 * stages + 2 + 4) * 8 + 16   # q_full, ring full/empty, s_full[2], p_full[2][2]
     return (Q_TILES + stages) * tile_bytes(head_dim) + barriers + 1024
 

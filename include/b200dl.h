@@ -179,6 +179,13 @@ const char* b200_last_error(void);
  * every kernel ran to completion, otherwise the code of the first bounded wait that gave
  * up.  Returns B200_OK / B200_ECUDA. */
 int b200_device_status(uint32_t* code);
+/* Self-test of the bounded waits every kernel of this library uses: launches a one-CTA kernel
+ * whose consumer waits for bytes its producer announced and never copied, with a limit of
+ * limit_ms (1..1000) milliseconds instead of the kernels' 2 s.  The wait gives up, the
+ * kernel returns, and the next b200_device_status() reports the non-zero code 0x80007e57;
+ * the device and the library stay usable.  No counterpart in the reference (its waits are
+ * unbounded). */
+int b200_selftest_wait_expiry(uint32_t limit_ms, void* stream);
 /* Library version string. */
 const char* b200_version(void);
 

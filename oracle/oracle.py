@@ -84,22 +84,16 @@ def use_all_cores():
     return num_threads()
 
 
-# ------------------------------------------------------------------ bit-pattern helpers
-def bf16_bits_from_f32(x):
-    """float32 array -> uint16 bf16 bit patterns, round-to-nearest-even."""
-    x = np.ascontiguousarray(x, dtype=np.float32)
-    u = x.view(np.uint32).astype(np.uint64)
-    rounded = (u + 0x7FFF + ((u >> 16) & 1)) >> 16
-    return rounded.astype(np.uint16)
+# Bit-pattern helpers and the seeded input generators live with the package (numpy only, no
+# oracle code involved) so that the benchmark's GPU arm can draw its inputs without loading
+# anything from this directory; they are re-exported here for the tests.
+import sys as _sys
 
-
-def f32_from_bf16_bits(b):
-    b = np.ascontiguousarray(b, dtype=np.uint16)
-    return (b.astype(np.uint32) << 16).view(np.float32)
-
-
-def f16_bits(x):
-    return np.ascontiguousarray(x, dtype=np.float16).view(np.uint16)
+_ROOT = os.path.dirname(_HERE)
+if _ROOT not in _sys.path:
+    _sys.path.insert(0, _ROOT)
+from sm120_dl_b200.synthetic import (bf16_bits_from_f32, f16_bits, f32_from_bf16_bits,  # noqa: E402,F401
+                                     make_fa_inputs, make_gemm_inputs)
 
 
 # ------------------------------------------------------------------------ C++ oracle
@@ -187,40 +181,3 @@ def attention_numpy(q_bits, k_bits, v_bits, causal=False, scale=None):
     p = np.exp(s)
     p /= p.sum(axis=-1, keepdims=True)
     return np.einsum("bhij,bjhd->bihd", p, v)
-
-
-# ------------------------------------------------------------------------ seeded inputs
-def make_gemm_inputs(M, N, K, seed, dist="normal_over_sqrt_k"):
-    """Deterministic bf16 operands as uint16 bit patterns, A first then B (the reference
-    fills A, B, C in that order: gemm/test.cpp:384-386).
-
-    dist: "uniform1" = uniform[-1,1) (512^3 case), "uniform01" = uniform[-0.1,0.1) (the
-    reference harness, gemm/test.cpp:384-386), "normal_over_sqrt_k" = N(0,1)/sqrt(K).
-    Generator: numpy PCG64(seed), float32 draws rounded to bf16.
-    """
-    rng = np.random.Generator(np.random.PCG64(seed))
-
-    def draw(rows):
-        if dist == "uniform1":
-            x = rng.uniform(-1.0, 1.0, size=(rows, K)).astype(np.float32)
-        elif dist == "uniform01":
-            x = rng.uniform(-0.1, 0.1, size=(rows, K)).astype(np.float32)
-        elif dist == "normal_over_sqrt_k":
-            x = rng.standard_normal(size=(rows, K), dtype=np.float32) / np.float32(np.sqrt(K))
-        else:
-            raise ValueError(dist)
-        return bf16_bits_from_f32(x)
-
-    a = draw(M)
-    b = draw(N)
-    return a, b
-
-
-def make_fa_inputs(B, S, H, D, seed, std=1.0):
-    """Deterministic fp16 q, k, v (in that order, verify.py:58-60) as uint16 patterns."""
-    rng = np.random.Generator(np.random.PCG64(seed))
-    out = []
-    for _ in range(3):
-        x = rng.standard_normal(size=(B, S, H, D), dtype=np.float32) * np.float32(std)
-        out.append(f16_bits(x))
-    return tuple(out)

@@ -39,7 +39,7 @@ EXPORTS = (
     "b200_gemm_bf16_tn_scatter",
     "b200_fa_num_configs", "b200_fa_get_config", "b200_fa_find_config",
     "b200_fa_default_config", "b200_fa_fwd_fp16", "b200_fa_fwd_fp16_scatter",
-    "b200_last_error", "b200_device_status", "b200_version",
+    "b200_last_error", "b200_device_status", "b200_selftest_wait_expiry", "b200_version",
 )
 
 _lib = None
@@ -96,6 +96,8 @@ def lib():
     L.b200_last_error.restype = ctypes.c_char_p
     L.b200_device_status.restype = ctypes.c_int
     L.b200_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint32)]
+    L.b200_selftest_wait_expiry.restype = ctypes.c_int
+    L.b200_selftest_wait_expiry.argtypes = [ctypes.c_uint32, vp]
     L.b200_version.restype = ctypes.c_char_p
     _lib = L
     return L

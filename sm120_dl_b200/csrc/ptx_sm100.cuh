@@ -101,20 +101,24 @@ struct WaitGuard {
 };
 
 // Returns false when the wait was abandoned (time limit hit here or elsewhere in the CTA).
-__device__ __forceinline__ bool mbar_wait_slow(const WaitGuard& g, uint32_t bar, uint32_t parity,
-                                            uint32_t site) {
+__device__ __forceinline__ bool mbar_wait_limit(const WaitGuard& g, uint32_t bar, uint32_t parity,
+                                             uint32_t site, unsigned long long limit_ns) {
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 0xffu) == 0) {
             if (*g.abort_flag != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *g.abort_flag = 1;
                 atomicCAS(g.status, 0u, 0x80000000u | site);
                 return false;
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait_slow(const WaitGuard& g, uint32_t bar, uint32_t parity,
+                                            uint32_t site) {
+    return mbar_wait_limit(g, bar, parity, site, kWaitLimitNs);
 }
 __device__ __forceinline__ bool mbar_wait(const WaitGuard& g, uint32_t bar, uint32_t parity,
                                           uint32_t site) {

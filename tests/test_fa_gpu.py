@@ -44,6 +44,16 @@ def _fwd(env, cfg, q, k, v, causal, out=None):
     return out
 
 
+def _layout_defaults(capi, head_dim):
+    """Index of the first config of every softmax layout for this head_dim (the first of them
+    is the library's default for the head_dim)."""
+    first = {}
+    for i, cfg in enumerate(capi.fa_configs()):
+        if cfg["head_dim"] == head_dim:
+            first.setdefault(cfg["softmax_layout"], i)
+    return sorted(first.values())
+
+
 # seq_len, head_dim, head_num, batch: the small entries of the reference's shape list
 # (verify.py:26-45) plus sizes that cross tile boundaries
 SMALL_SHAPES = [(64, 64, 1, 1), (128, 64, 1, 2), (192, 64, 4, 1), (256, 64, 8, 2), (128, 128, 4, 2),
@@ -75,17 +85,18 @@ def test_config3_b4_h32_s4096_d128(env):
     B, S, H, D = 4, 4096, 32, 128
     q_bits, k_bits, v_bits = oracle.make_fa_inputs(B, S, H, D, seed=2)
     q, k, v = (_dev(torch, x, dev) for x in (q_bits, k_bits, v_bits))
-    idx = lib.b200_fa_default_config(D)
-    o = _fwd(env, idx, q, k, v, False)
     rows = np.sort(np.random.Generator(np.random.PCG64(2)).choice(S, size=24, replace=False)).astype(np.int32)
     ref = oracle.attention_f32(q_bits, k_bits, v_bits, False, rows=rows)
-    err = np.abs(o[:, torch.from_numpy(rows).long().to(dev)].float().cpu().numpy() - ref).max()
-    assert err <= ABS_BOUND, err
     ones = torch.ones_like(v)
-    o1 = _fwd(env, idx, q, k, ones, False)
-    assert (o1.float() - 1.0).abs().max().item() <= 2e-3
-    # deterministic
-    assert torch.equal(o.view(torch.int16), _fwd(env, idx, q, k, v, False).view(torch.int16))
+    assert lib.b200_fa_default_config(D) in _layout_defaults(capi, D)
+    for idx in _layout_defaults(capi, D):
+        o = _fwd(env, idx, q, k, v, False)
+        err = np.abs(o[:, torch.from_numpy(rows).long().to(dev)].float().cpu().numpy() - ref).max()
+        assert err <= ABS_BOUND, (capi.fa_configs()[idx]["name"], err)
+        o1 = _fwd(env, idx, q, k, ones, False)
+        assert (o1.float() - 1.0).abs().max().item() <= 2e-3
+        # deterministic
+        assert torch.equal(o.view(torch.int16), _fwd(env, idx, q, k, v, False).view(torch.int16))
 
 
 def test_config4_b16_h32_s2048_d64(env):
@@ -93,11 +104,12 @@ def test_config4_b16_h32_s2048_d64(env):
     B, S, H, D = 16, 2048, 32, 64
     q_bits, k_bits, v_bits = oracle.make_fa_inputs(B, S, H, D, seed=3)
     q, k, v = (_dev(torch, x, dev) for x in (q_bits, k_bits, v_bits))
-    o = _fwd(env, lib.b200_fa_default_config(D), q, k, v, False)
     rows = np.sort(np.random.Generator(np.random.PCG64(3)).choice(S, size=12, replace=False)).astype(np.int32)
     ref = oracle.attention_f32(q_bits, k_bits, v_bits, False, rows=rows)
-    err = np.abs(o[:, torch.from_numpy(rows).long().to(dev)].float().cpu().numpy() - ref).max()
-    assert err <= ABS_BOUND, err
+    for idx in _layout_defaults(capi, D):
+        o = _fwd(env, idx, q, k, v, False)
+        err = np.abs(o[:, torch.from_numpy(rows).long().to(dev)].float().cpu().numpy() - ref).max()
+        assert err <= ABS_BOUND, (capi.fa_configs()[idx]["name"], err)
 
 
 def test_head_slices_through_strides(env):
@@ -107,11 +119,11 @@ def test_head_slices_through_strides(env):
     q_bits, k_bits, v_bits = oracle.make_fa_inputs(B, S, H, D, seed=21)
     ref = oracle.attention_f32(q_bits, k_bits, v_bits, True)
     q, k, v = (_dev(torch, x, dev) for x in (q_bits, k_bits, v_bits))
-    full = torch.full((B, S, H, D), float("nan"), dtype=torch.float16, device=dev)
-    idx = lib.b200_fa_default_config(D)
-    for h0 in range(0, H, 2):
-        _fwd(env, idx, q[:, :, h0:h0 + 2], k[:, :, h0:h0 + 2], v[:, :, h0:h0 + 2], True, out=full[:, :, h0:h0 + 2])
-    assert np.abs(full.float().cpu().numpy() - ref).max() <= ABS_BOUND
+    for idx in _layout_defaults(capi, D):
+        full = torch.full((B, S, H, D), float("nan"), dtype=torch.float16, device=dev)
+        for h0 in range(0, H, 2):
+            _fwd(env, idx, q[:, :, h0:h0 + 2], k[:, :, h0:h0 + 2], v[:, :, h0:h0 + 2], True, out=full[:, :, h0:h0 + 2])
+        assert np.abs(full.float().cpu().numpy() - ref).max() <= ABS_BOUND
 
 
 def test_large_scores_do_not_overflow(env):
@@ -121,10 +133,11 @@ def test_large_scores_do_not_overflow(env):
     q_bits, k_bits, v_bits = oracle.make_fa_inputs(B, S, H, D, seed=33, std=6.0)
     ref = oracle.attention_f32(q_bits, k_bits, v_bits, False)
     q, k, v = (_dev(torch, x, dev) for x in (q_bits, k_bits, v_bits))
-    o = _fwd(env, lib.b200_fa_default_config(D), q, k, v, False)
-    err = np.abs(o.float().cpu().numpy() - ref).max()
-    # outputs are O(6) here; fp16 output rounding alone is 2^-11 * 8
-    assert np.isfinite(err) and err <= 2e-2, err
+    for idx in _layout_defaults(capi, D):
+        o = _fwd(env, idx, q, k, v, False)
+        err = np.abs(o.float().cpu().numpy() - ref).max()
+        # outputs are O(6) here; fp16 output rounding alone is 2^-11 * 8
+        assert np.isfinite(err) and err <= 2e-2, (capi.fa_configs()[idx]["name"], err)
 
 
 def test_error_paths(env):

@@ -38,6 +38,9 @@ constexpr int kEpiBoxRows = 32;
 constexpr int kEpiBoxBytes = kEpiBoxRows * 128;  // 4 KiB: 32 rows x 64 bf16
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kMaxDst = 8;                  // copies of C one launch can write (one per GPU of a box)
+// Poll interval of an epilogue warp waiting for an accumulator (a mainloop of 8192 k-elements
+// lasts ~70 us; the other accumulator buffer hides this latency).
+constexpr unsigned kEpilogueSleepNs = 256;
 
 // Tensor maps of every destination of C.  With one entry this is the plain GEMM; with several,
 // each finished box is stored to all of them (own memory and peers' memory over NVLink), which
@@ -250,8 +253,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tile_coord(tile, tiles_m, tiles_n, bs_w, tm, tn);
             const uint32_t buf = local_tile % ACC_BUFS;
             const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
-            ok = mbar_wait(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf);
-            ok = __all_sync(0xffffffffu, ok);
+            ok = mbar_wait_warp_idle(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf, kEpilogueSleepNs);
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
                 if (is_leader && warp == 2 && lane == 0) mbar_arrive_remote(accfull_peer + 8 * buf);

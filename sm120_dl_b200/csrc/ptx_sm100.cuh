@@ -127,6 +127,35 @@ __device__ __forceinline__ bool mbar_wait(const WaitGuard& g, uint32_t bar, uint
     return mbar_wait_slow(g, bar, parity, site);
 }
 
+// A wait that is expected to last long (an epilogue warp waiting for the next tile's whole
+// mainloop): one lane polls, sleeping between polls, and the warp follows through
+// __syncwarp, so that 32 spinning lanes per warp do not draw power the tensor pipe could use.
+// Same bound and abort handling as mbar_wait; the result is warp-uniform.
+__device__ __forceinline__ bool mbar_wait_warp_idle(const WaitGuard& g, uint32_t bar, uint32_t parity,
+                                                    uint32_t site, unsigned sleep_ns) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        if (!mbar_try_wait(bar, parity)) {
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t it = 1;; ++it) {
+                __nanosleep(sleep_ns);
+                if (mbar_try_wait(bar, parity)) break;
+                if ((it & 0x3fu) == 0) {
+                    if (*g.abort_flag != 0) { ok = 0; break; }
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        *g.abort_flag = 1;
+                        atomicCAS(g.status, 0u, 0x80000000u | site);
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
 // The same guard with the abort flag held as a 32-bit shared-memory address (two registers
 // fewer in every role that waits; the attention kernel's softmax warps are register-bound).
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {

@@ -30,6 +30,10 @@ output columns <= 512.  The first config listed for a head dimension is its defa
 
 import argparse
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from genutil import write_if_changed  # noqa: E402
 
 HEAD_DIMS = (64, 128)
 TILE_Q = 128
@@ -101,36 +105,9 @@ def generate_configs(max_smem_kb, only=None):
     return configs
 
 
-class _write_if_changed:
-    """open(path, "w") that leaves the file (and its mtime) alone when the content is
-    unchanged, so a rebuild is triggered only by a real change of the config list."""
-
-    def __init__(self, path):
-        self.path = path
-        self.parts = []
-
-    def __enter__(self):
-        return self
-
-    def write(self, text):
-        self.parts.append(text)
-
-    def __exit__(self, *exc):
-        text = "".join(self.parts)
-        try:
-            with open(self.path, "r", encoding="utf-8") as f:
-                if f.read() == text:
-                    return False
-        except OSError:
-            pass
-        with open(self.path, "w", encoding="utf-8") as f:
-            f.write(text)
-        return False
-
-
 def write_inc(path, configs, max_smem_kb):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("// Auto-generated by flash_configs.py - do not edit\n")
         f.write(f"// {len(configs)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
         f.write("// B200_FA_CONFIG(name, HEAD_DIM, STAGES, EMU, LAYOUT, BLOCK_M, BLOCK_N)\n")
@@ -142,7 +119,7 @@ def write_registry(path, configs):
     """Entries of kFlashFwdConfigs[] for pybind/flash_fwd_config_registry.cpp, in the same
     order as the table inside libb200dl.so."""
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("// Auto-generated by flash_configs.py - do not edit\n")
         f.write("// B200_FA_ENTRY(index, name, HEAD_DIM, BLOCK_M, BLOCK_N, NWARPS, STAGES)\n")
         for i, (name, head_dim, stages, emu, layout, bm, bn) in enumerate(configs):
@@ -151,7 +128,7 @@ def write_registry(path, configs):
 
 def write_cmake(path, configs, max_smem_kb):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("# Auto-generated by flash_configs.py - do not edit\n")
         f.write(f"set(FLASH_FWD_MAX_SMEM_BYTES {max_smem_kb * 1024})\n")
         f.write("set(FLASH_FWD_CONFIGS\n")

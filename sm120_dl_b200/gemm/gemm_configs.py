@@ -27,6 +27,10 @@ GEMM_TN_MAX_SMEM_BYTES / GEMM_TN_CONFIGS / GEMM_TN_DEFAULT_CONFIG variables.
 
 import argparse
 import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from genutil import write_if_changed  # noqa: E402
 
 ELEMENT_BYTES = 2
 BK = 64                       # one 128-byte swizzle row of bf16
@@ -144,36 +148,9 @@ def generate_splitk_configs(max_smem_kb):
     return configs
 
 
-class _write_if_changed:
-    """open(path, "w") that leaves the file (and its mtime) alone when the content is
-    unchanged, so a rebuild is triggered only by a real change of the config list."""
-
-    def __init__(self, path):
-        self.path = path
-        self.parts = []
-
-    def __enter__(self):
-        return self
-
-    def write(self, text):
-        self.parts.append(text)
-
-    def __exit__(self, *exc):
-        text = "".join(self.parts)
-        try:
-            with open(self.path, "r", encoding="utf-8") as f:
-                if f.read() == text:
-                    return False
-        except OSError:
-            pass
-        with open(self.path, "w", encoding="utf-8") as f:
-            f.write(text)
-        return False
-
-
 def write_inc(path, configs, max_smem_kb, splitk=()):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("// Auto-generated by gemm_configs.py - do not edit\n")
         f.write(f"// {len(configs) + len(splitk)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
         f.write("// B200_GEMM_CONFIG(name, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)\n")
@@ -188,7 +165,7 @@ def write_registry(path, configs, splitk=()):
     """Entries of kGemmConfigs[] for gemm_config_registry.cpp: one line per config, the
     index being the config's position in libb200dl.so's own table."""
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("// Auto-generated by gemm_configs.py - do not edit\n")
         f.write("// B200_GEMM_ENTRY(index, name, BM, BN, BK, STAGES, CTA_GROUP, ACC_BUFS, BS_W)\n")
         for i, (name, bn, stages, cta_group, acc_bufs, bs_w) in enumerate(configs):
@@ -210,7 +187,7 @@ def write_cmake(path, configs, max_smem_kb):
         return "|".join(str(x) for x in ("bf16", "bf16", CTA_M * cta_group, bn, BK, stages,
                                          cta_group, acc_bufs, bs_w, name))
 
-    with _write_if_changed(path) as f:
+    with write_if_changed(path) as f:
         f.write("# Auto-generated by gemm_configs.py - do not edit\n")
         f.write(f"# {len(configs)} configs, max dynamic shared memory {max_smem_kb} KiB\n\n")
         f.write(f"set(GEMM_TN_MAX_SMEM_BYTES {max_smem_kb * 1024})\n")

@@ -91,6 +91,11 @@ def main():
     ap.add_argument("--func", default=None, help="profile a single config instead of reading BEST.txt")
     ap.add_argument("--shape", nargs=3, type=int, metavar=("M", "N", "K"), help="shape for --func")
     ap.add_argument("--only", default=None, help="comma-separated MxNxK filter")
+    ap.add_argument("--all", action="store_true",
+                    help="profile every BEST.txt entry; by default shapes whose operands exceed --max-gb are skipped")
+    ap.add_argument("--max-gb", type=float, default=1.0,
+                    help="largest A+B+C footprint profiled without --all or --only (multi-metric captures replay the "
+                         "kernel and save/restore device memory, so they belong on small cases)")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--out-dir", default=None, help="directory for .ncu-rep files (default: ./ncu_out)")
     args = ap.parse_args()
@@ -113,6 +118,12 @@ def main():
     if args.only:
         keep = {tuple(int(x) for x in s.lower().split("x")) for s in args.only.split(",")}
         entries = [e for e in entries if e[:3] in keep]
+    elif not args.all and not args.func:
+        small = [e for e in entries if 2.0 * (e[0] * e[2] + e[1] * e[2] + e[0] * e[1]) <= args.max_gb * 1e9]
+        for e in entries:
+            if e not in small:
+                print(f"# skipped {e[0]}x{e[1]}x{e[2]}: operands above {args.max_gb} GB (use --only or --all)")
+        entries = small
     if not entries:
         ap.error("no shapes to profile")
 

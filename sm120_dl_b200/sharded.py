@@ -43,15 +43,24 @@ def _world(group):
     return 1, 0
 
 
-def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None, config=None):
+def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None, config=None, out=None,
+                      root=None):
     """C = A @ B^T with the N dimension split across the ranks of `group`.
 
     a [M,K] is replicated; b is the FULL [N,K] matrix on every rank (each rank reads only
     its own row slab of it).  Returns (c, (n0, n1)): with gather=False c is this rank's
-    contiguous [M, n1-n0] slab; with gather=True c is the full [M,N] on every rank
-    (all-gather of the slabs, then a strided copy into place, because column slabs of a
-    row-major matrix are not contiguous).
+    contiguous [M, n1-n0] slab; with gather=True c is the full [M,N] on every rank.
+
+    The gather takes the fast path when the caller supplies the output as
+    out=(c_full, handle) from symmetric_empty(): the GEMM's epilogue then stores every
+    finished tile straight into the ranks' copies of c_full over NVLink (see
+    gemm_column_shard_fused; `root` limits the destinations to one rank).  Without such a
+    buffer it falls back to an NCCL all-gather of the slabs plus a strided copy into place
+    (column slabs of a row-major matrix are not contiguous).
     """
+    if gather and out is not None and compute is None:
+        c_full, handle = out
+        return gemm_column_shard_fused(a, b, c_full, handle, granule=granule, config=config, root=root)
     if compute is None:
         from . import ops
         compute = lambda x, y, out: ops.gemm_bf16_tn(x, y, out=out, config=config)  # noqa: E731
@@ -92,37 +101,47 @@ def symmetric_empty(shape, dtype, device, group=None):
     return t, handle
 
 
-def gemm_column_shard_fused(a, b, c_full, handle, granule=256, config=None, sync=True):
+def gemm_column_shard_fused(a, b, c_full, handle, granule=256, config=None, sync=True, root=None):
     """C = A @ B^T split by N-column blocks, with the gather fused into the GEMM's epilogue.
 
     `c_full` [M,N] and `handle` come from symmetric_empty(); each rank's kernel stores every
     finished tile of its column slab into ALL ranks' copies of c_full (TMA stores to peer
     memory), so when the ranks have synchronised every copy holds the full C -- no
-    all-gather, no staging buffer, no un-permute copy.  With sync=True the call ends with a
-    barrier over the group on the current stream; a caller that reuses c_full must also
-    keep readers of the previous contents ahead of the next call (same barrier).
+    all-gather, no staging buffer, no un-permute copy.  With `root` set, only rank `root`'s
+    copy is written ("the full output on one rank"): every other rank then sends its slab once
+    instead of world-1 times.  With sync=True the call ends with a barrier over the group on
+    the current stream; a caller that reuses c_full must also keep readers of the previous
+    contents ahead of the next call (same barrier).
     """
     from . import ops
     world, rank = handle.world_size, handle.rank
     M, N = c_full.shape
     n0, n1 = shard_bounds(N, world, rank, granule)
     if n1 > n0:
-        outs = [handle.get_buffer(r, (M, N), c_full.dtype)[:, n0:n1] for r in range(world)]
-        # own copy first: local stores start draining while the peer maps are touched
-        outs = outs[rank:] + outs[:rank]
+        targets = range(world) if root is None else [root]
+        outs = [handle.get_buffer(r, (M, N), c_full.dtype)[:, n0:n1] for r in targets]
+        if root is None:
+            # own copy first: local stores start draining while the peer maps are touched
+            outs = outs[rank:] + outs[:rank]
         ops.gemm_bf16_tn_scatter(a, b[n0:n1], outs, config=config)
     if sync:
         handle.barrier()
     return c_full, (n0, n1)
 
 
-def attention_head_shard(q, k, v, causal=False, group=None, gather=False, compute=None, config=None):
+def attention_head_shard(q, k, v, causal=False, group=None, gather=False, compute=None, config=None, out=None,
+                         root=None):
     """Attention forward with the heads split across the ranks of `group`.
 
     q, k, v are the FULL [B,S,H,D] tensors on every rank; each rank computes heads
     [h0, h1) through strided views.  Returns (o, (h0, h1)): with gather=False o is
-    [B,S,h1-h0,D]; with gather=True the full [B,S,H,D] on every rank.
+    [B,S,h1-h0,D]; with gather=True the full [B,S,H,D] on every rank -- through the fused
+    path when out=(o_full, handle) from symmetric_empty() is supplied, else through an NCCL
+    all-gather and a strided copy.
     """
+    if gather and out is not None and compute is None:
+        o_full, handle = out
+        return attention_head_shard_fused(q, k, v, o_full, handle, causal=causal, config=config, root=root)
     if compute is None:
         from . import ops
         compute = lambda x, y, z, c: ops.flash_attn_fwd(x, y, z, causal=c, config=config)  # noqa: E731
@@ -153,7 +172,7 @@ def attention_head_shard(q, k, v, causal=False, group=None, gather=False, comput
     return full, (h0, h1)
 
 
-def attention_head_shard_fused(q, k, v, o_full, handle, causal=False, config=None, sync=True):
+def attention_head_shard_fused(q, k, v, o_full, handle, causal=False, config=None, sync=True, root=None):
     """Attention with the heads split across ranks and the gather fused into the kernel's
     epilogue: each rank stores its heads' output tiles into ALL ranks' copies of `o_full`
     ([B,S,H,D] from symmetric_empty()).  Same synchronisation rules as
@@ -163,8 +182,10 @@ def attention_head_shard_fused(q, k, v, o_full, handle, causal=False, config=Non
     B, S, H, D = o_full.shape
     h0, h1 = shard_bounds(H, world, rank)
     if h1 > h0:
-        outs = [handle.get_buffer(r, (B, S, H, D), o_full.dtype)[:, :, h0:h1] for r in range(world)]
-        outs = outs[rank:] + outs[:rank]
+        targets = range(world) if root is None else [root]
+        outs = [handle.get_buffer(r, (B, S, H, D), o_full.dtype)[:, :, h0:h1] for r in targets]
+        if root is None:
+            outs = outs[rank:] + outs[:rank]
         ops.flash_attn_fwd_scatter(q[:, :, h0:h1], k[:, :, h0:h1], v[:, :, h0:h1], outs, causal=causal, config=config)
     if sync:
         handle.barrier()

@@ -164,25 +164,34 @@ fa_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant_
             uint32_t p_ph[2] = {0, 0};
             bool ok = true;
 
+            // Descriptors are built once per operand tile; a step of 16 along the head dimension
+            // (S) or of 16 key rows (P V) is a constant added to the address field, so one MMA
+            // costs two 64-bit adds beside the instruction itself (the issuing warp shares its
+            // scheduler with two softmax warps).
+            const uint64_t q_desc0 = smem_desc_kmajor_sw128(q_smem);
+            const uint64_t q_desc1 = smem_desc_kmajor_sw128(q_smem + T::kTileBytes);
             auto issue_s = [&](int i, uint32_t k_addr) {
-                const uint32_t q_addr = q_smem + i * T::kTileBytes;
+                const uint64_t q_desc = i ? q_desc1 : q_desc0;
+                const uint64_t k_desc = smem_desc_kmajor_sw128(k_addr);
                 if (!elect_one()) return;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-                    mma_ss<1>(tmem_base + T::kColS + i * kTileKV, smem_desc_kmajor_sw128(q_addr + off),
-                              smem_desc_kmajor_sw128(k_addr + off), idesc_qk, kk > 0 ? 1u : 0u);
+                    constexpr int kBoxUnits = kBoxBytes >> 4;
+                    const uint64_t off = static_cast<uint64_t>((kk >> 2) * kBoxUnits + (kk & 3) * 2);
+                    mma_ss<1>(tmem_base + T::kColS + i * kTileKV, q_desc + off, k_desc + off, idesc_qk,
+                              kk > 0 ? 1u : 0u);
                 }
             };
             // Part h of P V: 16-key steps [0,kSplitP) or [kSplitP,8) of the block.  P: 16 keys = 8 packed columns.
             // V: 16 key rows = 2048 bytes; the second 64-wide span of the head dimension lives
             // one box (16 KiB) further.
             auto issue_pv_half = [&](int i, int h, uint32_t v_addr, bool accumulate) {
+                const uint64_t v_desc = smem_desc_mnmajor_sw128(v_addr, kBoxBytes);
                 if (!elect_one()) return;
 #pragma unroll
                 for (int kk = (h ? kSplitP : 0); kk < (h ? 8 : kSplitP); ++kk) {
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
-                           smem_desc_mnmajor_sw128(v_addr + kk * 2048, kBoxBytes), idesc_pv,
+                           v_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
                            (accumulate || kk > 0) ? 1u : 0u);
                 }
             };

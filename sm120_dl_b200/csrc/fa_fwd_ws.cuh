@@ -46,13 +46,20 @@ constexpr int kWsRegsSoftmax = 96;        // warps 8-23: 64 scores of a row live
 static_assert(kWsRegsLoadMma * 128 + kWsRegsCorrection * 128 + kWsRegsSoftmax * 512 <= kWsRegsAtLaunch * kWsThreads,
               "setmaxnreg budgets exceed the registers the CTA is launched with");
 constexpr int kSmemLimit = 232448;        // 227 KiB
+// P of a block is handed to the MMA warp in two parts: the first after kPart0Steps 16-key steps
+// of either half of the row, the second at the end.
+#ifndef B200_FA_PART0_STEPS
+#define B200_FA_PART0_STEPS 2
+#endif
+constexpr int kPart0Steps = B200_FA_PART0_STEPS;
+static_assert(kPart0Steps >= 1 && kPart0Steps <= 3, "the first part is 16, 32 or 48 keys of each half");
 
 template <int D, int STAGES>
 struct FaWsTraits {
     static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
     static constexpr int kBoxes = D / 64;
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a Q tile, a K block or a V block
-    static constexpr int kNumBarriers = 2 + 2 * STAGES + 2 + 4 + 2 + 2 + 2 + 2 + 2;
+    static constexpr int kNumBarriers = 2 + 2 * STAGES + 2 + 4 + 8 + 2 + 2 + 2 + 2;
     // row maxima [2 block parities][2 tiles][2 halves][128] and row sums [2 tiles][2 halves][128], fp32
     static constexpr int kSmallBytes = 2 * 2 * 2 * kTileQ * 4 + 2 * 2 * kTileQ * 4 + kNumBarriers * 8 + 16;
     // tiles first (they need 1024-byte alignment for the 128-byte swizzle): Q, ring, one staging box
@@ -169,8 +176,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t kv_empty = kv_full + 8 * STAGES;       // [STAGES] MMA -> TMA
     const uint32_t s_full = kv_empty + 8 * STAGES;        // [2] MMA -> softmax: S_i ready
     const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: part h of P_i written
-    const uint32_t max_full = p_full + 32;                // [2] softmax -> softmax, correction: the block's row maxima published
-    const uint32_t o_ready = max_full + 16;               // [2] correction -> MMA: O_i may be accumulated into
+    const uint32_t max_full = p_full + 32;                // [2][4] softmax -> softmax, correction: the block's row maxima of
+                                                          // one tile and lane quadrant published (the two warps that share rows)
+    const uint32_t o_ready = max_full + 64;               // [2] correction -> MMA: O_i may be accumulated into
     const uint32_t o_final = o_ready + 16;                // [2] MMA -> correction: O_i of the unit complete
     const uint32_t sum_full = o_final + 16;               // [2] softmax -> correction: row sums published
     const uint32_t sum_empty = sum_full + 16;             // [2] correction -> softmax: row sums taken
@@ -192,7 +200,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             mbar_init(s_full + 8 * i, 1);
             mbar_init(p_full + 16 * i, 8);       // one arrival per softmax warp of the tile
             mbar_init(p_full + 16 * i + 8, 8);
-            mbar_init(max_full + 8 * i, 8);
+            for (int q = 0; q < 4; ++q) mbar_init(max_full + 32 * i + 8 * q, 2);   // the two column halves
             mbar_init(o_ready + 8 * i, 4);       // one arrival per correction warp
             mbar_init(o_final + 8 * i, 1);
             mbar_init(sum_full + 8 * i, 8);
@@ -284,18 +292,19 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
             };
             // Part h of P V.  The two threads of a row work on keys [0,64) and [64,128) at the
-            // same time, so the first part is the first 32 keys of either half: 16-key steps
-            // {0,1,4,5}, the second part steps {2,3,6,7}.  P: 16 keys = 8 packed columns.  V: 16
-            // key rows = 2048 bytes; the second 64-wide span of the head dimension lives one box
-            // (16 KiB) further.
+            // same time, so the first part is the first kPart0Steps 16-key steps of either half
+            // (steps 0.. of keys [0,64) and steps 4.. of keys [64,128)), the second part the
+            // rest.  P: 16 keys = 8 packed columns.  V: 16 key rows = 2048 bytes; the second
+            // 64-wide span of the head dimension lives one box (16 KiB) further.
             auto issue_pv_part = [&](int i, int h, uint64_t v_desc, bool accumulate) {
                 if (!elect_one()) return;
+                bool first = !accumulate;
 #pragma unroll
-                for (int x = 0; x < 4; ++x) {
-                    const int kk = (x >> 1) * 4 + 2 * h + (x & 1);
+                for (int kk = 0; kk < 8; ++kk) {
+                    if (((kk & 3) < kPart0Steps) != (h == 0)) continue;
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
-                           v_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv,
-                           (accumulate || x > 0) ? 1u : 0u);
+                           v_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv, first ? 0u : 1u);
+                    first = false;
                 }
             };
             auto commit = [&](uint32_t bar) {
@@ -413,7 +422,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         // from none.
         auto handle_block = [&](int i, bool first) {
             FA_PROF(1)
-            ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 8 * i, x_ph[i] & 1u, 0x1500u + i));
+            ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 32 * i + 8 * quad, x_ph[i] & 1u, 0x1500u + i));
             if (!ok) return;
             FA_PROF(0)
             const uint32_t box = max_smem + (((x_ph[i] & 1u) * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
@@ -575,8 +584,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 const uint32_t box = max_smem + ((par * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
                 st_shared_f32(box + half * kTileQ * 4, mine);
                 __syncwarp();
-                if (lane == 0) mbar_arrive(max_full + 8 * i);
-                ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 8 * i, par, 0x1308u + i));
+                if (lane == 0) mbar_arrive(max_full + 32 * i + 8 * quad);
+                ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 32 * i + 8 * quad, par, 0x1308u + i));
                 if (!ok) break;
                 const float theirs = ld_shared_f32(box + (half ^ 1) * kTileQ * 4);
                 // fmaxf in the order the correction thread uses (half 0, half 1)
@@ -588,23 +597,18 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 const float nm = -((m == -INFINITY) ? 0.f : m) * scale_log2;
                 const f32x2 nm2 = pack2(nm, nm);
                 uint32_t pr[8];
-                exp_16<EMU>(sa, pr, scale2, nm2, l, poly);
-                tmem_st_32x32b_x8(t_p, pr);              // keys 0..15 of this half -> 8 packed columns
-                exp_16<EMU>(sa + 16, pr, scale2, nm2, l, poly);
-                tmem_st_32x32b_x8(t_p + 8, pr);
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full + 16 * i);          // first 32 keys of both halves
-                FA_PROF(2)
-                exp_16<EMU>(sb, pr, scale2, nm2, l, poly);
-                tmem_st_32x32b_x8(t_p + 16, pr);
-                exp_16<EMU>(sb + 16, pr, scale2, nm2, l, poly);
-                tmem_st_32x32b_x8(t_p + 24, pr);
-                tmem_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full + 16 * i + 8);      // the rest
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    exp_16<EMU>((c < 2 ? sa : sb) + (c & 1) * 16, pr, scale2, nm2, l, poly);
+                    tmem_st_32x32b_x8(t_p + 8 * c, pr);      // 16 keys of this half -> 8 packed columns
+                    if (c == kPart0Steps - 1 || c == 3) {
+                        tmem_wait_st();
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(p_full + 16 * i + (c == 3 ? 8 : 0));
+                        if (c != 3) FA_PROF(2)
+                    }
+                }
                 FA_PROF(3)
             }
             if (!ok) break;

@@ -57,10 +57,10 @@ def tile_bytes(head_dim):
 
 def smem_bytes(head_dim, stages, layout):
     if layout == 2:
-        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2], o_ready[2],
+        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2][4], o_ready[2],
         # o_final[2], sum_full[2], sum_empty[2]; row maxima [2][2][2][128] and row sums
         # [2][2][128] in fp32; one 128 x 64 staging box for the output
-        barriers = (2 + 2 * stages + 2 + 4 + 2 + 2 + 2 + 2 + 2) * 8 + 16
+        barriers = (2 + 2 * stages + 2 + 4 + 8 + 2 + 2 + 2 + 2) * 8 + 16
         small = 2 * 2 * 2 * TILE_Q * 4 + 2 * 2 * TILE_Q * 4 + barriers
         return (Q_TILES + stages) * tile_bytes(head_dim) + 128 * 128 + small + 1024
     barriers = (1 + 2 * stages + 2 + 4) * 8 + 16   # q_full, ring full/empty, s_full[2], p_full[2][2]

@@ -62,6 +62,23 @@ int b200_gemm_find_config(const char* name);
  * measured efficiency of that MMA width.  Split-K configs are candidates only when the
  * tiles alone number fewer than 148 and every CTA of the cluster keeps >= 16 k-blocks. */
 int b200_gemm_default_config(int M, int N, int K);
+/* Stream-K for ragged last waves, off by default.  With mode 1 (process-wide), launches of the
+ * persistent configs cut the tiles of a last wave that would leave at least a tenth of the CTA
+ * groups idle along K over ALL groups (when every tile has >= 16 k-blocks and there are at
+ * least half as many tiles as groups): a group's share is the end of one tail tile (its fp32
+ * sums go to a workspace) and the beginning of the next (which it owns: it adds the following
+ * groups' sums in a fixed order, so results stay bit-reproducible, and stores the tile).  The
+ * workspace comes from a per-device pool (cudaMalloc on first use, ~20 MB; launches that can
+ * overlap never share one; at most 8 in flight per device); b200_gemm_bf16_tn_noalloc never
+ * cuts.  It is off by default because on B200 it did not pay on the shapes measured: tiles of
+ * one wave walk K in lockstep and share their A and B panels through L2, pieces that start
+ * at different k-blocks do not, and the fix-up runs at the very end of the kernel where
+ * nothing hides it (16384x512x4096: 61 us against 57 us).  No counterpart in the reference
+ * (its tile loop hands out whole tiles, gemm/gemm_cute.hpp:121).
+ * b200_gemm_uses_stream_k: 1 when a launch of this config and shape would cut its last wave
+ * under the current mode on the current device. */
+int b200_gemm_set_stream_k(int mode);
+int b200_gemm_uses_stream_k(int config, int M, int N, int K);
 
 /* C[M,N] = A[M,K] * B[N,K]^T, bf16 operands, fp32 accumulation, bf16 round-to-nearest-even
  * output, C fully overwritten (alpha = 1, beta = 0).  Row-major with leading dimensions

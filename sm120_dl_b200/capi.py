@@ -35,7 +35,8 @@ class FaConfig(ctypes.Structure):
 
 EXPORTS = (
     "b200_gemm_num_configs", "b200_gemm_get_config", "b200_gemm_find_config",
-    "b200_gemm_default_config", "b200_gemm_bf16_tn", "b200_gemm_f16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_noalloc_status",
+    "b200_gemm_default_config", "b200_gemm_set_stream_k", "b200_gemm_uses_stream_k",
+    "b200_gemm_bf16_tn", "b200_gemm_f16_tn", "b200_gemm_bf16_tn_noalloc", "b200_gemm_noalloc_status",
     "b200_gemm_bf16_tn_scatter",
     "b200_fa_num_configs", "b200_fa_get_config", "b200_fa_find_config",
     "b200_fa_default_config", "b200_fa_fwd_fp16", "b200_fa_fwd_fp16_scatter",
@@ -64,6 +65,10 @@ def lib():
     L.b200_gemm_find_config.argtypes = [ctypes.c_char_p]
     L.b200_gemm_default_config.restype = ctypes.c_int
     L.b200_gemm_default_config.argtypes = [ctypes.c_int] * 3
+    L.b200_gemm_set_stream_k.restype = ctypes.c_int
+    L.b200_gemm_set_stream_k.argtypes = [ctypes.c_int]
+    L.b200_gemm_uses_stream_k.restype = ctypes.c_int
+    L.b200_gemm_uses_stream_k.argtypes = [ctypes.c_int] * 4
     L.b200_gemm_bf16_tn.restype = ctypes.c_int
     L.b200_gemm_bf16_tn.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                     vp, i64, vp, i64, vp, i64, vp]

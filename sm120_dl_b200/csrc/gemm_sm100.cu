@@ -20,6 +20,7 @@
 //
 // A second kernel, gemm_splitk_kernel, serves shapes with too few tiles to occupy the GPU: a
 // cluster of CTAs shares one tile along K and sums its partials through distributed shared memory.
+#include <atomic>
 #include <cstdio>
 #include <cstring>
 #include <mutex>
@@ -82,12 +83,72 @@ __device__ __forceinline__ void tile_coord(int tile, int tiles_m, int tiles_n, i
     tn = n0 + r - tm * w;
 }
 
+// ---------------------------------------------------------------- work items of a CTA group
+// A CTA (pair) walks `full_waves` whole tiles (tile ids group, group + groups, ...).  The tiles
+// of a ragged last wave are either handed out whole (tail_tiles of the groups take one more)
+// or, with stream-K, cut along K: the tail tiles' k-blocks form one sequence that is divided
+// evenly over all groups, so every group gets the same amount of work.  A group's share
+// touches at most two tail tiles: the end of one (a *partial* piece: its fp32 sums go to a
+// workspace slot of that group) and the beginning of the next (an *owner* piece: it starts
+// at k-block 0, adds the partial pieces the following groups wrote for this tile, in group
+// order, and stores the tile).  A partial piece is always a group's first tail item and an
+// owner piece its last, and partial pieces wait for nobody, so owners never wait in a cycle.
+struct StreamKPlan {
+    int full_waves;     // whole tiles per group before the tail
+    int tail_tiles;     // tiles of the ragged last wave (0: none, or not split)
+    int enabled;        // 1: the tail is cut along K
+    float* partials;    // [groups][CTA_GROUP][BN/4][128 rows][4] fp32 sums of partial pieces
+    uint32_t* flags;    // [groups][CTA_GROUP][4 epilogue warps]: == epoch when that warp's rows are written
+    uint32_t epoch;
+};
+
+struct WorkItem {
+    int tile;           // tile id (rasterised by tile_coord)
+    int kb_begin, kb_end;
+    int kind;           // 0 whole tile, 1 owner piece (adds partials of the next groups), 2 partial piece
+};
+
+// Item `it` of `group`, or false when the group has no more work.
+__device__ __forceinline__ bool work_item(const StreamKPlan& plan, int group, int groups, int num_tiles, int k_blocks,
+                                          int it, WorkItem& w) {
+    if (it < plan.full_waves) {
+        w = WorkItem{group + it * groups, 0, k_blocks, 0};
+        return true;
+    }
+    const int t = it - plan.full_waves;
+    if (!plan.enabled) {
+        // whole tail tiles to the first groups
+        if (t > 0 || group >= num_tiles - plan.full_waves * groups) return false;
+        w = WorkItem{plan.full_waves * groups + group, 0, k_blocks, 0};
+        return true;
+    }
+    // this group's share [seg_begin, seg_end) of the tail's k-blocks (units of one k-block)
+    const long units = static_cast<long>(plan.tail_tiles) * k_blocks;
+    const long seg_begin = units * group / groups;
+    const long seg_end = units * (group + 1) / groups;
+    const int first_tile = static_cast<int>(seg_begin / k_blocks);
+    const long first_end = static_cast<long>(first_tile + 1) * k_blocks;
+    const int base = plan.full_waves * groups;
+    if (t == 0) {
+        if (seg_end <= seg_begin) return false;
+        const int kb0 = static_cast<int>(seg_begin - static_cast<long>(first_tile) * k_blocks);
+        const int kb1 = static_cast<int>((seg_end < first_end ? seg_end : first_end) - static_cast<long>(first_tile) * k_blocks);
+        w = WorkItem{base + first_tile, kb0, kb1, kb0 == 0 ? 1 : 2};
+        return true;
+    }
+    if (t == 1 && seg_end > first_end) {
+        w = WorkItem{base + first_tile + 1, 0, static_cast<int>(seg_end - first_end), 1};
+        return true;
+    }
+    return false;
+}
+
 template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CMapSet tmap_c, int n_dst, int M, int N, int K, int bs_w,
-                    int is_bf16,
+                    int is_bf16, const StreamKPlan plan,
                     uint32_t* status) {
     using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
     constexpr int BM = kCtaM * CTA_GROUP;
@@ -163,12 +224,13 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t ph = 0;
             uint32_t fills = 0;  // ring slots filled so far by this CTA
             bool ok = true;
-            for (int tile = group; tile < num_tiles && ok; tile += num_groups) {
+            WorkItem item;
+            for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it) {
                 int tm, tn;
-                tile_coord(tile, tiles_m, tiles_n, bs_w, tm, tn);
+                tile_coord(item.tile, tiles_m, tiles_n, bs_w, tm, tn);
                 const int row_a = tm * BM + static_cast<int>(cta_rank) * kCtaM;
                 const int row_b = tn * BN + static_cast<int>(cta_rank) * T::kBRows;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
                     ok = mbar_wait(guard, empty_bar + 8 * s, ph ^ 1u, 0x100u + s);
                     if (!ok) break;
                     if constexpr (CTA_GROUP == 2) {
@@ -209,14 +271,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             uint32_t ph = 0;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int tile = group; tile < num_tiles && ok; tile += num_groups, ++local_tile) {
+            WorkItem item;
+            for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
                 const uint32_t buf = local_tile % ACC_BUFS;
                 const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8 * buf, acc_ph ^ 1u, 0x200u + buf));
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
                     ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s));
                     if (!ok) break;
                     tc_fence_after();
@@ -228,7 +291,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                             // 16 elements of K = 32 bytes inside the swizzled row = +2 in the
                             // descriptor's 16-byte address units.
                             mma_ss<CTA_GROUP>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc,
-                                              (kb | k) != 0 ? 1u : 0u);
+                                              (kb != item.kb_begin || k != 0) ? 1u : 0u);
                         }
                         mma_commit<CTA_GROUP>(empty_bar + 8 * s);
                     }
@@ -248,9 +311,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t local_tile = 0;
         uint32_t stores = 0;
         bool ok = true;
-        for (int tile = group; tile < num_tiles && ok; tile += num_groups, ++local_tile) {
+        WorkItem item;
+        for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
             int tm, tn;
-            tile_coord(tile, tiles_m, tiles_n, bs_w, tm, tn);
+            tile_coord(item.tile, tiles_m, tiles_n, bs_w, tm, tn);
             const uint32_t buf = local_tile % ACC_BUFS;
             const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
             ok = mbar_wait_warp_idle(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf, kEpilogueSleepNs);
@@ -261,6 +325,28 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             tc_fence_after();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
             const int out_row = tm * BM + static_cast<int>(cta_rank) * kCtaM + q * 32;
+            // Stream-K: where this warp's 32 rows of a partial piece live in the workspace, as
+            // [column group of 4][row][4 floats] so that the lanes of a warp touch 512 contiguous
+            // bytes; slot = (group, CTA of the pair).
+            constexpr int kSlotFloats = (BN / 4) * kCtaM * 4;
+            const int row_in_cta = q * 32 + lane;
+            int n_contrib = 0;
+            if (item.kind == 1 && item.kb_end < k_blocks) {
+                // an owner piece that stops short of the last k-block: the following groups hold the
+                // rest of this tile as their first (partial) pieces.  Count them, then wait for this
+                // warp's rows of each (they were started before this piece and wait for nobody).
+                const long units = static_cast<long>(plan.tail_tiles) * k_blocks;
+                const long tile_end = static_cast<long>(item.tile - plan.full_waves * num_groups + 1) * k_blocks;
+                for (int g = group + 1; g < num_groups; ++g) {
+                    ++n_contrib;
+                    if (units * (g + 1) / num_groups >= tile_end) break;
+                }
+                for (int g = group + 1; g <= group + n_contrib && ok; ++g) {
+                    const uint32_t* flag = plan.flags + (static_cast<size_t>(g) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - 2);
+                    ok = wait_flag_warp(guard, flag, plan.epoch, 0x500u);
+                }
+                if (!ok) break;
+            }
 #pragma unroll 1
             for (int c = 0; c < BN / 64; ++c) {
                 uint32_t acc0[32], acc1[32];
@@ -277,6 +363,49 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         } else {
                             mbar_arrive(accempty_bar + 8 * buf);
                         }
+                    }
+                }
+                if (item.kind == 2) {
+                    // partial piece: park the fp32 sums for the tile's owner
+                    float4* dst = reinterpret_cast<float4*>(plan.partials) +
+                                  (static_cast<size_t>(group) * CTA_GROUP + cta_rank) * (kSlotFloats / 4) +
+                                  static_cast<size_t>(c * 16) * kCtaM + row_in_cta;
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        dst[static_cast<size_t>(g4) * kCtaM] =
+                            make_float4(__uint_as_float(acc0[4 * g4]), __uint_as_float(acc0[4 * g4 + 1]),
+                                        __uint_as_float(acc0[4 * g4 + 2]), __uint_as_float(acc0[4 * g4 + 3]));
+                        dst[static_cast<size_t>(8 + g4) * kCtaM] =
+                            make_float4(__uint_as_float(acc1[4 * g4]), __uint_as_float(acc1[4 * g4 + 1]),
+                                        __uint_as_float(acc1[4 * g4 + 2]), __uint_as_float(acc1[4 * g4 + 3]));
+                    }
+                    if (c == BN / 64 - 1) {
+                        // every row of this warp is written: publish (release) to the owner's warp q
+                        __threadfence();
+                        __syncwarp();
+                        if (lane == 0)
+                            st_release_gpu_u32(plan.flags + (static_cast<size_t>(group) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - 2),
+                                               plan.epoch);
+                    }
+                    continue;
+                }
+                for (int g = group + 1; g <= group + n_contrib; ++g) {
+                    // add the partial sums of the following groups, in group order (deterministic)
+                    const float4* src = reinterpret_cast<const float4*>(plan.partials) +
+                                        (static_cast<size_t>(g) * CTA_GROUP + cta_rank) * (kSlotFloats / 4) +
+                                        static_cast<size_t>(c * 16) * kCtaM + row_in_cta;
+#pragma unroll
+                    for (int g4 = 0; g4 < 8; ++g4) {
+                        const float4 u = ld_global_cg_f4(src + static_cast<size_t>(g4) * kCtaM);
+                        const float4 v = ld_global_cg_f4(src + static_cast<size_t>(8 + g4) * kCtaM);
+                        acc0[4 * g4] = __float_as_uint(__uint_as_float(acc0[4 * g4]) + u.x);
+                        acc0[4 * g4 + 1] = __float_as_uint(__uint_as_float(acc0[4 * g4 + 1]) + u.y);
+                        acc0[4 * g4 + 2] = __float_as_uint(__uint_as_float(acc0[4 * g4 + 2]) + u.z);
+                        acc0[4 * g4 + 3] = __float_as_uint(__uint_as_float(acc0[4 * g4 + 3]) + u.w);
+                        acc1[4 * g4] = __float_as_uint(__uint_as_float(acc1[4 * g4]) + v.x);
+                        acc1[4 * g4 + 1] = __float_as_uint(__uint_as_float(acc1[4 * g4 + 1]) + v.y);
+                        acc1[4 * g4 + 2] = __float_as_uint(__uint_as_float(acc1[4 * g4 + 2]) + v.z);
+                        acc1[4 * g4 + 3] = __float_as_uint(__uint_as_float(acc1[4 * g4 + 3]) + v.w);
                     }
                 }
                 uint32_t packed[32];
@@ -530,6 +659,99 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 }
 
 // ------------------------------------------------------------------------- host launcher
+// Workspaces of stream-K launches: fp32 partial tiles and their flags.  Kept in a small
+// per-device pool; each carries the stream and the event of the last launch that used it.  A
+// launch takes the one last used on its own stream (stream order already keeps those
+// kernels apart), else the first one whose event has completed, else a new one, so launches
+// that can overlap never share a workspace.  Flags are compared with a per-
+// workspace epoch that grows with every launch, so they never need clearing.
+struct StreamKWorkspace {
+    float* partials = nullptr;
+    uint32_t* flags = nullptr;
+    size_t partial_bytes = 0, flag_bytes = 0;
+    uint32_t epoch = 0;
+    cudaEvent_t done = nullptr;
+    cudaStream_t last_stream = nullptr;
+    bool in_use = false;      // taken by a launch that has not recorded its event yet
+};
+constexpr int kMaxWorkspaces = 8;
+StreamKWorkspace g_workspaces[kMaxDevices][kMaxWorkspaces];
+std::mutex g_workspace_mutex;
+
+StreamKWorkspace* acquire_stream_k_workspace(int device, cudaStream_t stream, size_t partial_bytes,
+                                             size_t flag_bytes) {
+    std::lock_guard<std::mutex> lock(g_workspace_mutex);
+    StreamKWorkspace* free_slot = nullptr;
+    for (int i = 0; i < kMaxWorkspaces; ++i) {
+        StreamKWorkspace& w = g_workspaces[device][i];
+        if (!w.in_use && w.partials != nullptr && w.last_stream == stream && w.partial_bytes >= partial_bytes &&
+            w.flag_bytes >= flag_bytes) {
+            w.in_use = true;
+            return &w;
+        }
+    }
+    for (int i = 0; i < kMaxWorkspaces; ++i) {
+        StreamKWorkspace& w = g_workspaces[device][i];
+        if (w.in_use) continue;
+        if (w.partials == nullptr) {
+            if (free_slot == nullptr) free_slot = &w;
+            continue;
+        }
+        if (cudaEventQuery(w.done) != cudaSuccess) {
+            (void)cudaGetLastError();   // cudaErrorNotReady: still running
+            continue;
+        }
+        if (w.partial_bytes < partial_bytes || w.flag_bytes < flag_bytes) {
+            // idle but too small: replace it
+            cudaFree(w.partials);
+            cudaFree(w.flags);
+            w.partials = nullptr;
+            w.flags = nullptr;
+            if (free_slot == nullptr) free_slot = &w;
+            continue;
+        }
+        w.in_use = true;
+        return &w;
+    }
+    if (free_slot == nullptr) {
+        fail(B200_ECUDA, "more than %d stream-K launches in flight on device %d", kMaxWorkspaces, device);
+        return nullptr;
+    }
+    StreamKWorkspace& w = *free_slot;
+    cudaError_t e = cudaMalloc(reinterpret_cast<void**>(&w.partials), partial_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void**>(&w.flags), flag_bytes);
+    if (e == cudaSuccess) e = cudaMemset(w.flags, 0, flag_bytes);
+    if (e == cudaSuccess && w.done == nullptr) e = cudaEventCreateWithFlags(&w.done, cudaEventDisableTiming);
+    if (e != cudaSuccess) {
+        fail(B200_ECUDA, "stream-K workspace (%zu bytes): %s", partial_bytes + flag_bytes, cudaGetErrorString(e));
+        if (w.partials) cudaFree(w.partials);
+        if (w.flags) cudaFree(w.flags);
+        w.partials = nullptr;
+        w.flags = nullptr;
+        return nullptr;
+    }
+    w.partial_bytes = partial_bytes;
+    w.flag_bytes = flag_bytes;
+    w.epoch = 0;
+    w.in_use = true;
+    return &w;
+}
+
+void release_stream_k_workspace(StreamKWorkspace* w, cudaStream_t stream) {
+    std::lock_guard<std::mutex> lock(g_workspace_mutex);
+    (void)cudaEventRecord(w->done, stream);
+    w->last_stream = stream;
+    w->in_use = false;
+}
+
+// Whether a launch with this many tiles, CTA groups and k-blocks cuts its last wave along K.
+std::atomic<int> g_stream_k_mode{0};   // b200_gemm_set_stream_k: 0 = off (default), 1 = on
+bool wants_stream_k(int num_tiles, int groups, int k_blocks) {
+    if (g_stream_k_mode.load(std::memory_order_relaxed) == 0) return false;
+    const int tail = num_tiles % groups;
+    return tail > 0 && tail * 10 <= groups * 9 && k_blocks >= 16 && num_tiles * 2 >= groups;
+}
+
 using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
                          int64_t, const void*, int64_t, void* const*, int, int64_t, bool, cudaStream_t);
 
@@ -570,8 +792,31 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
 
     const int num_tiles = ((M + kCtaM * CTA_GROUP - 1) / (kCtaM * CTA_GROUP)) * ((N + BN - 1) / BN);
+    const int k_blocks = (K + kBK - 1) / kBK;
     int groups = dev->sm_count / CTA_GROUP;
-    if (groups > num_tiles) groups = num_tiles;
+
+    // Ragged last wave: cut its tiles along K over all groups (stream-K) when that saves more
+    // than the fix-up costs -- at least a tenth of a tile time per group, tiles long enough to
+    // amortise parking and re-reading a partial tile, and not the few-tile regime the cluster
+    // split-K kernel serves.  The workspace comes from a per-device pool: a launch takes one
+    // whose previous launch has finished (or a new one), so overlapping launches never share.
+    StreamKPlan plan{};
+    const bool stream_k = dev->may_allocate && wants_stream_k(num_tiles, groups, k_blocks);
+    if (!stream_k && groups > num_tiles) groups = num_tiles;
+    plan.full_waves = num_tiles / groups;
+    plan.tail_tiles = num_tiles % groups;
+    StreamKWorkspace* ws = nullptr;
+    if (stream_k) {
+        const size_t slot_bytes = static_cast<size_t>(BN) * kCtaM * sizeof(float);
+        const size_t partial_bytes = static_cast<size_t>(groups) * CTA_GROUP * slot_bytes;
+        const size_t flag_bytes = static_cast<size_t>(groups) * CTA_GROUP * kEpiWarps * sizeof(uint32_t);
+        ws = acquire_stream_k_workspace(dev->device, stream, partial_bytes, flag_bytes);
+        if (ws == nullptr) return B200_ECUDA;
+        plan.enabled = 1;
+        plan.partials = ws->partials;
+        plan.flags = ws->flags;
+        plan.epoch = ++ws->epoch;
+    }
 
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(static_cast<unsigned>(groups * CTA_GROUP), 1, 1);
@@ -586,7 +831,8 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     lc.attrs = attr;
     lc.numAttrs = 1;
     cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tmap_a, tmap_b, tmap_c, n_dst, M, N, K, cfg.bs_w,
-                                       is_bf16 ? 1 : 0, dev->status);
+                                       is_bf16 ? 1 : 0, plan, dev->status);
+    if (ws != nullptr) release_stream_k_workspace(ws, stream);
     if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
     return B200_OK;
 }
@@ -751,6 +997,7 @@ const DeviceInfo* noalloc_device() {
         return nullptr;
     }
     info.status = static_cast<uint32_t*>(scratch);
+    info.may_allocate = false;
     slot.info = info;
     slot.ready = true;
     return &slot.info;
@@ -774,6 +1021,23 @@ int b200_gemm_find_config(const char* name) {
         if (std::strcmp(name, b200::kEntries[i].cfg.name) == 0) return i;
     }
     return -1;
+}
+
+int b200_gemm_set_stream_k(int mode) {
+    if (mode != 0 && mode != 1) return b200::fail(B200_EINVAL, "stream-K mode must be 0 or 1 (got %d)", mode);
+    b200::g_stream_k_mode.store(mode, std::memory_order_relaxed);
+    return B200_OK;
+}
+
+int b200_gemm_uses_stream_k(int config, int M, int N, int K) {
+    using namespace b200;
+    if (config < 0 || config >= kNumEntries || M <= 0 || N <= 0 || K <= 0) return 0;
+    const b200_gemm_config& c = kEntries[config].cfg;
+    if (c.split_k > 1) return 0;
+    int sms = current_sm_count();
+    if (sms <= 0) sms = 148;
+    const int tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+    return wants_stream_k(tiles, sms / c.cta_group, (K + c.bk - 1) / c.bk) ? 1 : 0;
 }
 
 int b200_gemm_default_config(int M, int N, int K) {

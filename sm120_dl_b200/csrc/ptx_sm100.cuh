@@ -156,6 +156,51 @@ __device__ __forceinline__ bool mbar_wait_warp_idle(const WaitGuard& g, uint32_t
     return ok != 0;
 }
 
+// ------------------------------------------------------------------ global-memory flags
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// 16-byte load that bypasses L1 (data another CTA wrote during this launch).
+__device__ __forceinline__ float4 ld_global_cg_f4(const float4* p) {
+    float4 v;
+    asm volatile("ld.global.cg.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(p)
+                 : "memory");
+    return v;
+}
+// One lane polls a flag in global memory until it holds `want` (written with
+// st_release_gpu_u32 by another CTA of the same launch); the warp follows.  Bounded like
+// every wait here: gives up after kWaitLimitNs or when the CTA's abort flag is up.
+__device__ __forceinline__ bool wait_flag_warp(const WaitGuard& g, const uint32_t* flag, uint32_t want, uint32_t site) {
+    uint32_t ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        if (ld_acquire_gpu_u32(flag) != want) {
+            const uint64_t t0 = globaltimer_ns();
+            for (uint32_t it = 1;; ++it) {
+                __nanosleep(64);
+                if (ld_acquire_gpu_u32(flag) == want) break;
+                if ((it & 0x3fu) == 0) {
+                    if (*g.abort_flag != 0) { ok = 0; break; }
+                    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                        *g.abort_flag = 1;
+                        atomicCAS(g.status, 0u, 0x80000000u | site);
+                        ok = 0;
+                        break;
+                    }
+                }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
 // The same guard with the abort flag held as a 32-bit shared-memory address (two registers
 // fewer in every role that waits; the attention kernel's softmax warps are register-bound).
 __device__ __forceinline__ uint32_t ld_shared_u32(uint32_t addr) {

@@ -20,6 +20,7 @@ struct DeviceInfo {
     int cc_major = 0;
     int max_smem_optin = 0;
     uint32_t* status = nullptr;  // one zero-initialised word block in device memory
+    bool may_allocate = true;    // false for the allocation-free entry point: no stream-ordered workspace
 };
 
 // Facts about the CURRENT device (the reference hard-codes device 0 for its SM-count query,

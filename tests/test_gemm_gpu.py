@@ -320,3 +320,83 @@ def test_split_k_leading_dimensions_several_row_tiles_ragged_k(env):
         _check(oracle, wide[:, 104:104 + N].float().cpu().numpy(), ref)
         # nothing outside the slab was touched
         assert bool((wide[:, :104] == -7.0).all()) and bool((wide[:, 104 + N:] == -7.0).all()), name
+
+
+@pytest.fixture
+def stream_k(env):
+    """Stream-K switched on for one test (it is off by default), and off again afterwards."""
+    lib = env[2]
+    assert lib.b200_gemm_set_stream_k(1) == 0
+    yield
+    assert lib.b200_gemm_set_stream_k(0) == 0
+
+
+def test_stream_k_is_off_by_default(env):
+    torch, capi, lib, oracle, dev = env
+    idx = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
+    assert lib.b200_gemm_uses_stream_k(idx, 2560, 2560, 2048) == 0
+    assert lib.b200_gemm_set_stream_k(2) == -1
+    assert lib.b200_gemm_set_stream_k(1) == 0
+    assert lib.b200_gemm_uses_stream_k(idx, 2560, 2560, 2048) == 1
+    assert lib.b200_gemm_uses_stream_k(idx, 2560, 2560, 512) == 0     # 8 k-blocks: too short to pay
+    assert lib.b200_gemm_set_stream_k(0) == 0
+
+
+@pytest.mark.parametrize("shape", [(2560, 2560, 1024), (1280, 2560, 2048), (2500, 2440, 1096), (16384, 512, 4096)],
+                         ids=lambda s: "%dx%dx%d" % s)
+def test_ragged_last_wave_is_cut_along_k(env, stream_k, shape):
+    """Shapes whose tiles do not fill the last wave, with stream-K on: the launcher splits the
+    tail tiles' k-blocks over all CTA groups, partial sums go through a workspace and are added
+    in a fixed order.  Every element against the oracle, run-to-run bitwise equality, for
+    CTA-pair and single-CTA configs, and through the multi-destination entry point."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = shape
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 11)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    rows = min(M, 2560)
+    ref = oracle.gemm_f64(a_bits, b_bits, row_begin=M - rows, row_count=rows)
+    cut = 0
+    for name in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn256_bk64_s4_cta1_acc2_bsw8",
+                 "bf16_bm256_bn128_bk64_s8_cta2_acc2_bsw8"):
+        idx = lib.b200_gemm_find_config(name.encode())
+        assert idx >= 0
+        cut += lib.b200_gemm_uses_stream_k(idx, M, N, K)
+        c = _run(env, idx, a, b, M, N, K)
+        _check(oracle, c[M - rows:].float().cpu().numpy(), ref)
+        assert bool(torch.isfinite(c.float()).all())
+        again = _run(env, idx, a, b, M, N, K)
+        assert torch.equal(c.view(torch.int16), again.view(torch.int16)), name
+        # two destinations at once
+        outs = [torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ptrs = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in outs])
+        rc = lib.b200_gemm_bf16_tn_scatter(idx, M, N, K, a.data_ptr(), K, b.data_ptr(), K, ptrs, 2, N, None)
+        assert rc == 0, lib.b200_last_error().decode()
+        assert capi.device_status() == 0
+        for t in outs:
+            assert torch.equal(t.view(torch.int16), c.view(torch.int16)), name
+    assert cut >= 1, "none of the configs cut this shape's last wave: the test shape no longer exercises stream-K"
+
+
+def test_stream_k_overlapping_streams(env, stream_k):
+    """Launches on two streams at once: every launch has its own stream-ordered workspace."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = 2560, 2560, 2048
+    idx = lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8")
+    assert lib.b200_gemm_uses_stream_k(idx, M, N, K) == 1
+    streams = [torch.cuda.Stream(device=dev) for _ in range(2)]
+    problems = []
+    for i, st in enumerate(streams):
+        a_bits, b_bits = oracle.make_gemm_inputs(M, N, K, 20 + i)
+        a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+        c = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev)
+        problems.append((a_bits, b_bits, a, b, c))
+    torch.cuda.synchronize()
+    for rep in range(6):
+        for (a_bits, b_bits, a, b, c), st in zip(problems, streams):
+            rc = lib.b200_gemm_bf16_tn(idx, M, N, K, a.data_ptr(), K, b.data_ptr(), K, c.data_ptr(), N,
+                                       ctypes.c_void_p(st.cuda_stream))
+            assert rc == 0, lib.b200_last_error().decode()
+    torch.cuda.synchronize()
+    assert capi.device_status() == 0
+    for a_bits, b_bits, a, b, c in problems:
+        _check(oracle, c[:256].float().cpu().numpy(), oracle.gemm_f64(a_bits, b_bits, row_begin=0, row_count=256))

@@ -524,7 +524,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (next_has[i]) handle_block(i, true);
             }
         }
-        if (lane == 0) tma_store_wait_all<0>();
+        if (lane == 0) tma_store_wait_read<0>();   // shared memory may go; the writes finish on their own before the grid does
         if (warp == 4) FA_PROF_DUMP(24)
     } else {
         setmaxnreg_inc<kWsRegsSoftmax>();

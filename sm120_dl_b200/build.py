@@ -2,6 +2,8 @@
 
   libb200dl.so            csrc/*.cu  -> the C ABI library (sm_100a only)
   gemm/test_gemm_cute     the reference-compatible GEMM harness (C++), links libb200dl.so
+  gemm/test_gemm_multi_gpu  the N-column-sharded GEMM over the GPUs of one box (C++, one thread
+                          per device, NCCL for the baseline gather)
   flashatten_v3_sm120.so  the pybind/torch extension mirroring the reference's module
 
 Run as `python -m sm120_dl_b200.build [targets...]`; with no targets everything is built.
@@ -119,6 +121,21 @@ def build_test_gemm_cute(force=False, verbose=False):
     return out
 
 
+def build_test_gemm_multi_gpu(force=False, verbose=False):
+    src = os.path.join(GEMM_DIR, "multi_gpu_gemm.cpp")
+    out = os.path.join(GEMM_DIR, "test_gemm_multi_gpu")
+    if not os.path.exists(src):
+        return None
+    deps = [src, os.path.join(ROOT, "include", "b200dl.h"), LIB]
+    if force or _newer(deps, out):
+        tmp = out + ".tmp"
+        _run([NVCC] + NVCC_FLAGS + ["-x", "cu", src, "-I", os.path.join(ROOT, "include"), "-o", tmp, "-L", HERE,
+              "-lb200dl", "-lcublas", "-lnccl", "-Xcompiler", "-pthread", "-Xlinker", "-rpath", "-Xlinker",
+              "$ORIGIN/.."], verbose)
+        os.replace(tmp, out)
+    return out
+
+
 def build_fa_module(force=False, verbose=False):
     src = os.path.join(FA_DIR, "pybind", "flashatten_v3_pybind.cpp")
     if not os.path.exists(src):
@@ -154,6 +171,7 @@ def build_fa_module(force=False, verbose=False):
 def build_all(force=False, verbose=False):
     outs = {"lib": build_lib(force, verbose)}
     outs["test_gemm_cute"] = build_test_gemm_cute(force, verbose)
+    outs["test_gemm_multi_gpu"] = build_test_gemm_multi_gpu(force, verbose)
     outs["fa_module"] = build_fa_module(force, verbose)
     return outs
 
@@ -172,6 +190,9 @@ if __name__ == "__main__":
         elif t == "test_gemm_cute":
             build_lib(False, verbose)
             print(build_test_gemm_cute(force, verbose))
+        elif t == "test_gemm_multi_gpu":
+            build_lib(False, verbose)
+            print(build_test_gemm_multi_gpu(force, verbose))
         elif t == "fa_module":
             build_lib(False, verbose)
             print(build_fa_module(force, verbose))

@@ -39,9 +39,6 @@ constexpr int kEpiBoxRows = 32;
 constexpr int kEpiBoxBytes = kEpiBoxRows * 128;  // 4 KiB: 32 rows x 64 bf16
 constexpr int kThreads = 32 * (2 + kEpiWarps);
 constexpr int kMaxDst = 8;                  // copies of C one launch can write (one per GPU of a box)
-// Poll interval of an epilogue warp waiting for an accumulator (a mainloop of 8192 k-elements
-// lasts ~70 us; the other accumulator buffer hides this latency).
-constexpr unsigned kEpilogueSleepNs = 256;
 
 // Tensor maps of every destination of C.  With one entry this is the plain GEMM; with several,
 // each finished box is stored to all of them (own memory and peers' memory over NVLink), which
@@ -52,11 +49,17 @@ struct CMapSet {
 
 constexpr int tmem_cols_for(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : n <= 256 ? 256 : 512; }
 
-template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+// MH = 128-row halves of A a CTA works on per tile (1 or 2).  With 2, a CTA owns two
+// accumulators of the same B tile: the output tile is 256 * CTA_GROUP rows tall, every B block
+// loaded from L2 feeds twice the arithmetic (a quarter fewer operand bytes per flop than the
+// 256 x 256 pair tile), and the two accumulators fill all 512 tensor-memory columns, so the
+// epilogue overlaps the next tile's mainloop by one accumulator instead of a whole tile.
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS, int MH = 1>
 struct GemmTraits {
     static constexpr int kBRows = BN / CTA_GROUP;        // B rows this CTA loads per stage
     static constexpr int kBStageBytes = kBRows * 128;
-    static constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+    static constexpr int kACtaStageBytes = MH * kAStageBytes;
+    static constexpr int kStageBytes = kACtaStageBytes + kBStageBytes;
     static constexpr int kRingBytes = STAGES * kStageBytes;
     static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBoxBytes;
     static constexpr int kBarrierBytes = (2 * STAGES + 2 * ACC_BUFS) * 8 + 16;
@@ -66,6 +69,7 @@ struct GemmTraits {
     static_assert(BN % 64 == 0 && BN >= 64 && BN <= 256, "BN must be 64, 128, 192 or 256");
     static_assert(ACC_BUFS * BN <= 512, "accumulators exceed the 512 tensor-memory columns");
     static_assert(CTA_GROUP == 1 || CTA_GROUP == 2, "CTA_GROUP must be 1 or 2");
+    static_assert(MH == 1 || (MH == 2 && ACC_BUFS == 2), "two A halves use one accumulator each");
     static_assert(kBRows % 8 == 0, "B rows per CTA must be a multiple of the 8-row swizzle group");
     static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB shared-memory limit of sm_100");
 };
@@ -143,20 +147,21 @@ __device__ __forceinline__ bool work_item(const StreamKPlan& plan, int group, in
     return false;
 }
 
-template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS, int MH>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CMapSet tmap_c, int n_dst, int M, int N, int K, int bs_w,
                     int is_bf16, const StreamKPlan plan,
                     uint32_t* status) {
-    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
-    constexpr int BM = kCtaM * CTA_GROUP;
+    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS, MH>;
+    constexpr int kHalfM = kCtaM * CTA_GROUP;   // rows one MMA instruction covers
+    constexpr int BM = kHalfM * MH;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t ring_a = smem_base;
-    const uint32_t ring_b = smem_base + STAGES * kAStageBytes;
+    const uint32_t ring_b = smem_base + STAGES * T::kACtaStageBytes;
     const uint32_t epi_base = smem_base + T::kRingBytes;
     const uint32_t bar_base = epi_base + T::kEpiBytes;
     const uint32_t full_bar = bar_base;                      // [STAGES] TMA -> MMA
@@ -245,13 +250,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         mbar_arrive_expect_tx(full_bar + 8 * s, T::kStageBytes * CTA_GROUP);
                     }
                     if constexpr (CTA_GROUP == 2) {
-                        tma_load_2d_pair(ring_a + s * kAStageBytes, &tmap_a, full_leader + 8 * s,
-                                         kb * kBK, row_a);
+#pragma unroll
+                        for (int h = 0; h < MH; ++h) {
+                            tma_load_2d_pair(ring_a + s * T::kACtaStageBytes + h * kAStageBytes, &tmap_a,
+                                             full_leader + 8 * s, kb * kBK, row_a + h * kHalfM);
+                        }
                         tma_load_2d_pair(ring_b + s * T::kBStageBytes, &tmap_b, full_leader + 8 * s,
                                          kb * kBK, row_b);
                     } else {
-                        tma_load_2d(ring_a + s * kAStageBytes, &tmap_a, full_bar + 8 * s, kb * kBK,
-                                    row_a);
+#pragma unroll
+                        for (int h = 0; h < MH; ++h) {
+                            tma_load_2d(ring_a + s * T::kACtaStageBytes + h * kAStageBytes, &tmap_a,
+                                        full_bar + 8 * s, kb * kBK, row_a + h * kHalfM);
+                        }
                         tma_load_2d(ring_b + s * T::kBStageBytes, &tmap_b, full_bar + 8 * s, kb * kBK,
                                     row_b);
                     }
@@ -266,13 +277,51 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         // warp-uniform code costs fewer issue cycles than from a single diverged lane.
         if (is_leader) {
             // operand format: bf16 (1) or fp16 (0); the accumulator is fp32 either way
-            const uint32_t idesc = make_idesc_f16(BM, BN, is_bf16 ? 1 : 0, 0, 0);
+            const uint32_t idesc = make_idesc_f16(kHalfM, BN, is_bf16 ? 1 : 0, 0, 0);
             int s = 0;
             uint32_t ph = 0;
             uint32_t local_tile = 0;
             bool ok = true;
             WorkItem item;
             for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
+                if constexpr (MH == 2) {
+                    // Both accumulators belong to this tile: accumulator h is free once the
+                    // epilogue has drained the previous tile's half h, so the first k-block's
+                    // MMAs into half 0 run while half 1 is still being drained.
+                    const uint32_t acc_ph = local_tile & 1u;
+                    for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
+                        ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s));
+                        if (!ok) break;
+                        const bool first = (kb == item.kb_begin);
+                        const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + s * T::kACtaStageBytes);
+                        const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + s * T::kBStageBytes);
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (first) {
+                                ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8 * h, acc_ph ^ 1u, 0x200u + h));
+                                if (!ok) break;
+                            }
+                            tc_fence_after();
+                            if (elect_one()) {
+#pragma unroll
+                                for (int k = 0; k < kBK / 16; ++k) {
+                                    mma_ss<CTA_GROUP>(tmem_base + h * BN, a_desc + (h * (kAStageBytes >> 4) + 2 * k),
+                                                      b_desc + 2 * k, idesc, (!first || k != 0) ? 1u : 0u);
+                                }
+                                if (h == 1) mma_commit<CTA_GROUP>(empty_bar + 8 * s);
+                            }
+                            __syncwarp();
+                        }
+                        if (!ok) break;
+                        if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    }
+                    if (ok && elect_one()) {
+                        mma_commit<CTA_GROUP>(accfull_bar);
+                        mma_commit<CTA_GROUP>(accfull_bar + 8);
+                    }
+                    __syncwarp();
+                    continue;
+                }
                 const uint32_t buf = local_tile % ACC_BUFS;
                 const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8 * buf, acc_ph ^ 1u, 0x200u + buf));
@@ -315,16 +364,19 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
             int tm, tn;
             tile_coord(item.tile, tiles_m, tiles_n, bs_w, tm, tn);
-            const uint32_t buf = local_tile % ACC_BUFS;
-            const uint32_t acc_ph = (local_tile / ACC_BUFS) & 1u;
-            ok = mbar_wait_warp_idle(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf, kEpilogueSleepNs);
+#pragma unroll 1
+          for (int h = 0; h < MH; ++h) {   // the tile's accumulators, drained one after the other
+            const uint32_t buf = (MH == 2) ? static_cast<uint32_t>(h) : local_tile % ACC_BUFS;
+            const uint32_t acc_ph = (MH == 2) ? (local_tile & 1u) : ((local_tile / ACC_BUFS) & 1u);
+            // a long wait (a whole mainloop): the hardware parks the warp, see mbar_wait_limit
+            ok = __all_sync(0xffffffffu, mbar_wait(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf));
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
                 if (is_leader && warp == 2 && lane == 0) mbar_arrive_remote(accfull_peer + 8 * buf);
             }
             tc_fence_after();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
-            const int out_row = tm * BM + static_cast<int>(cta_rank) * kCtaM + q * 32;
+            const int out_row = tm * BM + h * kHalfM + static_cast<int>(cta_rank) * kCtaM + q * 32;
             // Stream-K: where this warp's 32 rows of a partial piece live in the workspace, as
             // [column group of 4][row][4 floats] so that the lanes of a warp touch 512 contiguous
             // bytes; slot = (group, CTA of the pair).
@@ -346,6 +398,63 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     ok = wait_flag_warp(guard, flag, plan.epoch, 0x500u);
                 }
                 if (!ok) break;
+            }
+            if constexpr (MH == 2) {
+                // The next tile's mainloop waits for this accumulator: read and round all of it
+                // first (128 packed registers per thread), hand it back, then stage and store.
+                uint32_t packed[BN / 64][32];
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t acc0[32], acc1[32];
+                    tmem_ld_32x32b_x32(t_row + c * 64, acc0);
+                    tmem_ld_32x32b_x32(t_row + c * 64 + 32, acc1);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const float a0 = __uint_as_float(acc0[2 * i]), a1 = __uint_as_float(acc0[2 * i + 1]);
+                        const float b0 = __uint_as_float(acc1[2 * i]), b1 = __uint_as_float(acc1[2 * i + 1]);
+                        if (is_bf16) {
+                            __nv_bfloat162 v0 = __floats2bfloat162_rn(a0, a1);
+                            __nv_bfloat162 v1 = __floats2bfloat162_rn(b0, b1);
+                            packed[c][i] = *reinterpret_cast<uint32_t*>(&v0);
+                            packed[c][16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                        } else {
+                            __half2 v0 = __floats2half2_rn(a0, a1);
+                            __half2 v1 = __floats2half2_rn(b0, b1);
+                            packed[c][i] = *reinterpret_cast<uint32_t*>(&v0);
+                            packed[c][16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if constexpr (CTA_GROUP == 2) {
+                        mbar_arrive_remote(accempty_leader + 8 * buf);
+                    } else {
+                        mbar_arrive(accempty_bar + 8 * buf);
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < BN / 64; ++c) {
+                    const uint32_t box = my_epi + (stores & 1u) * kEpiBoxBytes;
+                    if (lane == 0) tma_store_wait_read<1>();
+                    __syncwarp();
+                    const uint32_t row_addr = box + lane * 128;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        st_shared_v4(row_addr + ((j ^ (lane & 7)) << 4), packed[c][4 * j], packed[c][4 * j + 1],
+                                     packed[c][4 * j + 2], packed[c][4 * j + 3]);
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        for (int d = 0; d < n_dst; ++d) tma_store_2d(&tmap_c.m[d], box, tn * BN + c * 64, out_row);
+                        tma_store_commit();
+                    }
+                    ++stores;
+                }
+                continue;
             }
 #pragma unroll 1
             for (int c = 0; c < BN / 64; ++c) {
@@ -443,6 +552,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
                 ++stores;
             }
+          }
         }
         if (lane == 0) tma_store_wait_all<0>();
     }
@@ -755,12 +865,13 @@ bool wants_stream_k(int num_tiles, int groups, int k_blocks) {
 using LaunchFn = int (*)(const DeviceInfo*, const b200_gemm_config&, int, int, int, const void*,
                          int64_t, const void*, int64_t, void* const*, int, int64_t, bool, cudaStream_t);
 
-template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS>
+template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS, int MH = 1>
 int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N, int K,
                 const void* A, int64_t lda, const void* B, int64_t ldb, void* const* C_list, int n_dst,
                 int64_t ldc, bool is_bf16, cudaStream_t stream) {
-    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>;
-    auto kernel = gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC_BUFS>;
+    using T = GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS, MH>;
+    auto kernel = gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC_BUFS, MH>;
+    constexpr int BM = kCtaM * CTA_GROUP * MH;
 
     CUtensorMap tmap_a, tmap_b;
     CMapSet tmap_c;
@@ -791,7 +902,7 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     static bool attr_done[kMaxDevices] = {};
     if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
 
-    const int num_tiles = ((M + kCtaM * CTA_GROUP - 1) / (kCtaM * CTA_GROUP)) * ((N + BN - 1) / BN);
+    const int num_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
     const int k_blocks = (K + kBK - 1) / kBK;
     int groups = dev->sm_count / CTA_GROUP;
 
@@ -801,7 +912,8 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
     // split-K kernel serves.  The workspace comes from a per-device pool: a launch takes one
     // whose previous launch has finished (or a new one), so overlapping launches never share.
     StreamKPlan plan{};
-    const bool stream_k = dev->may_allocate && wants_stream_k(num_tiles, groups, k_blocks);
+    // (tiles with two accumulators per CTA are never cut: both accumulators are in use)
+    const bool stream_k = MH == 1 && dev->may_allocate && wants_stream_k(num_tiles, groups, k_blocks);
     if (!stream_k && groups > num_tiles) groups = num_tiles;
     plan.full_waves = num_tiles / groups;
     plan.tail_tiles = num_tiles % groups;
@@ -935,6 +1047,11 @@ struct Entry {
                            GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kSmemBytes,                    \
                            GemmTraits<BN, STAGES, CTA_GROUP, ACC_BUFS>::kTmemCols, 1},                 \
           &launch_gemm<BN, STAGES, CTA_GROUP, ACC_BUFS>, nullptr},
+#define B200_GEMM_TALL_CONFIG(NAME, BN, STAGES, BS_W)                                                  \
+    Entry{b200_gemm_config{NAME, kCtaM * 4, BN, kBK, STAGES, 2, 2, BS_W,                               \
+                           GemmTraits<BN, STAGES, 2, 2, 2>::kSmemBytes,                                \
+                           GemmTraits<BN, STAGES, 2, 2, 2>::kTmemCols, 1},                             \
+          &launch_gemm<BN, STAGES, 2, 2, 2>, nullptr},
 #define B200_GEMM_SPLITK_CONFIG(NAME, BN, STAGES, SPLIT_K)                                             \
     Entry{b200_gemm_config{NAME, kCtaM, BN, kBK, STAGES, 1, 1, 1, SplitKTraits<BN, STAGES>::kSmemBytes, \
                            SplitKTraits<BN, STAGES>::kTmemCols, SPLIT_K},                              \
@@ -944,6 +1061,7 @@ const Entry kEntries[] = {
 #include "generated/gemm_configs.inc"
 };
 #undef B200_GEMM_CONFIG
+#undef B200_GEMM_TALL_CONFIG
 #undef B200_GEMM_SPLITK_CONFIG
 
 constexpr int kNumEntries = static_cast<int>(sizeof(kEntries) / sizeof(kEntries[0]));
@@ -1033,7 +1151,7 @@ int b200_gemm_uses_stream_k(int config, int M, int N, int K) {
     using namespace b200;
     if (config < 0 || config >= kNumEntries || M <= 0 || N <= 0 || K <= 0) return 0;
     const b200_gemm_config& c = kEntries[config].cfg;
-    if (c.split_k > 1) return 0;
+    if (c.split_k > 1 || c.bm > 128 * c.cta_group) return 0;   // split-K and tall tiles are never cut
     int sms = current_sm_count();
     if (sms <= 0) sms = 148;
     const int tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
@@ -1071,6 +1189,11 @@ int b200_gemm_default_config(int M, int N, int K) {
         const long ctas = tiles * c.cta_group * c.split_k;
         const long active = ctas < sms ? ctas : sms;
         double t_kb = c.bn >= 256 ? (c.cta_group == 2 ? 0.40 : 0.43) : c.bn >= 192 ? 0.36 : c.bn >= 128 ? 0.29 : 0.22;
+        // Tall tiles (two accumulators per CTA): twice the work per k-block at a quarter fewer
+        // operand bytes per flop, which under the power cap is worth 3-7 % on long problems
+        // (measured: 8192^3 +7 %, K = 4096 shapes +1-3 %); their epilogue overlaps less.
+        const int halves = c.bm / (128 * c.cta_group);
+        if (halves == 2) t_kb *= 2.0 * 0.97;
         if (ctas < sms || c.split_k > 1) {
             const double bytes = (128.0 + c.bn / c.cta_group) * 128.0;                 // A and B rows of one k-block
             const double gbs = 95.0 < 11500.0 / active ? 95.0 : 11500.0 / active;       // per CTA
@@ -1080,12 +1203,13 @@ int b200_gemm_default_config(int M, int N, int K) {
         const double kb_per_cta = static_cast<double>((kb + c.split_k - 1) / c.split_k);
         // persistent kernels overlap all but the last epilogue with the next tile's mainloop
         const double fixed = c.split_k > 1 ? (c.split_k == 8 ? 12.0 : 8.0 + 0.25 * c.split_k)
-                                           : (c.acc_bufs > 1 ? 4.0 : 4.0 + 1.5 * (waves - 1)) +
+                                           : (halves == 2 ? 4.0 + 0.8 * (waves - 1)
+                                              : c.acc_bufs > 1 ? 4.0 : 4.0 + 1.5 * (waves - 1)) +
                                                  // the pair handshake per tile shows on latency-bound problems
                                                  ((c.cta_group == 2 && tiles < sms / 2) ? 1.0 : 0.0);
         double cost = waves * kb_per_cta * t_kb + fixed;
-        // ties: deeper ring, strip width 8 (fastest measured on 8192^3)
-        cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == 8 ? 0.0002 : 0.0);
+        // ties: deeper ring; strip width 8 (16 for tall tiles), fastest measured on 8192^3
+        cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == (halves == 2 ? 16 : 8) ? 0.0002 : 0.0);
         if (best < 0 || cost < best_cost) {
             best_cost = cost;
             best = i;

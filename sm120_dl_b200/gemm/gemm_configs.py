@@ -18,6 +18,12 @@ vocabulary is Blackwell's: instead of warp grids for mma.sync it chooses
               accumulates its share of K and the partial tiles are summed through
               distributed shared memory
 
+  tall tiles  512 x bn tiles of a CTA pair: each CTA works on two 128-row halves of A against
+              the same B block, one accumulator per half (all 512 tensor-memory columns), so a B
+              block fetched from L2 feeds twice the arithmetic: a quarter fewer operand bytes
+              per flop than the 256 x 256 pair tile, at the price of an epilogue that overlaps
+              the next mainloop by one accumulator instead of a whole tile
+
 Legality is decided by the hardware budgets of one SM: 227 KiB of shared memory, 512
 tensor-memory columns, tcgen05.mma shape rules.  Two files are written: a C include with
 one B200_GEMM_CONFIG(...) line per config (compiled into libb200dl.so) and, for drop-in
@@ -148,20 +154,55 @@ def generate_splitk_configs(max_smem_kb):
     return configs
 
 
-def write_inc(path, configs, max_smem_kb, splitk=()):
+TALL_BN_VALUES = (256,)
+TALL_STAGE_VALUES = (3, 4)
+# a wave of 74 tile pairs is closest to square (fewest distinct A and B rows) at 12 tiles x 6
+TALL_BS_W_VALUES = (8, 12, 16)
+
+
+def tall_smem_bytes(bn, stages):
+    barrier_bytes = (2 * stages + 4) * 8 + 16
+    stage = (2 * CTA_M * BK + (bn // 2) * BK) * ELEMENT_BYTES
+    return stages * stage + EPILOGUE_BYTES + barrier_bytes + ALIGN_SLACK
+
+
+def tall_config_name(bn, stages, bs_w):
+    return f"bf16_bm{4 * CTA_M}_bn{bn}_bk{BK}_s{stages}_cta2_acc2_bsw{bs_w}"
+
+
+def generate_tall_configs(max_smem_kb):
+    """Returns a list of (name, bn, stages, bs_w): CTA-pair configs with two accumulators per
+    CTA (512-row tiles), every ring depth that fits, every strip width."""
+    max_smem = max_smem_kb * 1024
+    configs = []
+    for bn in TALL_BN_VALUES:
+        if 2 * bn > TMEM_COLUMNS:
+            continue
+        for stages in TALL_STAGE_VALUES:
+            if tall_smem_bytes(bn, stages) > max_smem:
+                continue
+            for bs_w in TALL_BS_W_VALUES:
+                configs.append((tall_config_name(bn, stages, bs_w), bn, stages, bs_w))
+    return configs
+
+
+def write_inc(path, configs, max_smem_kb, splitk=(), tall=()):
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
     with write_if_changed(path) as f:
         f.write("// Auto-generated by gemm_configs.py - do not edit\n")
-        f.write(f"// {len(configs) + len(splitk)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
+        f.write(f"// {len(configs) + len(splitk) + len(tall)} configs, max dynamic shared memory {max_smem_kb} KiB\n")
         f.write("// B200_GEMM_CONFIG(name, BN, STAGES, CTA_GROUP, ACC_BUFS, BS_W)\n")
         for name, bn, stages, cta_group, acc_bufs, bs_w in configs:
             f.write(f'B200_GEMM_CONFIG("{name}", {bn}, {stages}, {cta_group}, {acc_bufs}, {bs_w})\n')
         f.write("// B200_GEMM_SPLITK_CONFIG(name, BN, STAGES, SPLIT_K)\n")
         for name, bn, stages, split_k in splitk:
             f.write(f'B200_GEMM_SPLITK_CONFIG("{name}", {bn}, {stages}, {split_k})\n')
+        f.write("// B200_GEMM_TALL_CONFIG(name, BN, STAGES, BS_W)\n")
+        for name, bn, stages, bs_w in tall:
+            f.write(f'B200_GEMM_TALL_CONFIG("{name}", {bn}, {stages}, {bs_w})\n')
 
 
-def write_registry(path, configs, splitk=()):
+def write_registry(path, configs, splitk=(), tall=()):
     """Entries of kGemmConfigs[] for gemm_config_registry.cpp: one line per config, the
     index being the config's position in libb200dl.so's own table."""
     os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
@@ -175,6 +216,8 @@ def write_registry(path, configs, splitk=()):
             # bk = 64 * split_k: "K divisible by bk" is how the harness decides run vs skipped,
             # and a split-K config needs at least one k-block per CTA of its cluster
             f.write(f'B200_GEMM_ENTRY({i}, "{name}", {CTA_M}, {bn}, {BK * split_k}, {stages}, 1, 1, 1)\n')
+        for i, (name, bn, stages, bs_w) in enumerate(tall, start=len(configs) + len(splitk)):
+            f.write(f'B200_GEMM_ENTRY({i}, "{name}", {4 * CTA_M}, {bn}, {BK}, {stages}, 2, 2, {bs_w})\n')
 
 
 def write_cmake(path, configs, max_smem_kb):
@@ -215,11 +258,12 @@ def main(argv=None):
     if not configs:
         raise RuntimeError("no valid GEMM configs generated")
     splitk = generate_splitk_configs(args.max_smem_kb)
-    write_inc(args.inc, configs, args.max_smem_kb, splitk)
-    write_registry(args.registry, configs, splitk)
+    tall = generate_tall_configs(args.max_smem_kb)
+    write_inc(args.inc, configs, args.max_smem_kb, splitk, tall)
+    write_registry(args.registry, configs, splitk, tall)
     if args.output:
         write_cmake(args.output, configs, args.max_smem_kb)
-    print(f"Generated {len(configs)} + {len(splitk)} split-K configs -> {os.path.normpath(args.inc)}")
+    print(f"Generated {len(configs)} + {len(splitk)} split-K + {len(tall)} tall configs -> {os.path.normpath(args.inc)}")
     return configs
 
 

@@ -87,7 +87,7 @@ def test_identity_b_reproduces_a_exactly(env):
     a = _to_dev(torch, a_bits, dev, torch.bfloat16)
     eye = torch.eye(N, K, dtype=torch.bfloat16, device=dev)
     for name in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn128_bk64_s6_cta1_acc2_bsw8",
-                 "bf16_bm256_bn64_bk64_s8_cta2_acc2_bsw8"):
+                 "bf16_bm256_bn64_bk64_s8_cta2_acc2_bsw8", "bf16_bm512_bn256_bk64_s4_cta2_acc2_bsw16"):
         c = _run(env, lib.b200_gemm_find_config(name.encode()), a, eye, M, N, K)
         assert torch.equal(c.view(torch.int16), a.view(torch.int16)), name
 
@@ -105,6 +105,45 @@ def test_deterministic_and_many_tiles_per_cta(env):
         c2 = _run(env, idx, a, b, M, N, K)
         assert torch.equal(c1.view(torch.int16), c2.view(torch.int16))
         _check(oracle, c1.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("shape", [(8192, 3584, 192), (8062, 3600, 200), (1536, 520, 1096)])
+def test_tall_tiles_two_accumulators_per_cta(env, shape):
+    """512 x 256 tiles (two 128-row halves of A per CTA against one B block): up to four tiles
+    per CTA pair, so both accumulators are reused and their barriers change phase; K shorter
+    than the ring; ragged M, N and K; a column slab of a wider C; two destinations."""
+    torch, capi, lib, oracle, dev = env
+    M, N, K = shape
+    lda = (K + 7) // 8 * 8
+    a_bits, b_bits = oracle.make_gemm_inputs(M, N, lda, 31)
+    a, b = _to_dev(torch, a_bits, dev, torch.bfloat16), _to_dev(torch, b_bits, dev, torch.bfloat16)
+    rows = min(M, 1200)
+    ref = oracle.gemm_f64(a_bits[:, :K].copy(), b_bits[:, :K].copy(), row_begin=M - rows, row_count=rows)
+    first = None
+    for name in ("bf16_bm512_bn256_bk64_s4_cta2_acc2_bsw16", "bf16_bm512_bn256_bk64_s3_cta2_acc2_bsw12"):
+        idx = lib.b200_gemm_find_config(name.encode())
+        assert idx >= 0 and lib.b200_gemm_uses_stream_k(idx, M, N, K) == 0
+        ldc = (N + 7) // 8 * 8 + 64
+        wide = torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device=dev)
+        _run(env, idx, a, b, M, N, K, c=wide, lda=lda, ldb=lda, ldc=ldc)
+        c = wide[:, :N]
+        assert bool(torch.isnan(wide[:, N:].float()).all()), "wrote outside its column slab"
+        _check(oracle, c[M - rows:].float().cpu().numpy(), ref)
+        assert bool(torch.isfinite(c.float()).all())
+        if first is None:
+            first = c.clone()
+        assert torch.equal(c.contiguous().view(torch.int16), first.contiguous().view(torch.int16)), name
+        outs = [torch.full((M, ldc), float("nan"), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+        ptrs = (ctypes.c_void_p * 2)(*[t.data_ptr() for t in outs])
+        rc = lib.b200_gemm_bf16_tn_scatter(idx, M, N, K, a.data_ptr(), lda, b.data_ptr(), lda, ptrs, 2, ldc, None)
+        assert rc == 0, lib.b200_last_error().decode()
+        assert capi.device_status() == 0
+        for t in outs:
+            assert torch.equal(t[:, :N].contiguous().view(torch.int16), first.contiguous().view(torch.int16)), name
+    # the 256 x 256 tile computes the same sums in the same order: bit-identical
+    base = _run(env, lib.b200_gemm_find_config(b"bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8"), a, b, M, N, K,
+                lda=lda, ldb=lda)
+    assert torch.equal(base.view(torch.int16), first.contiguous().view(torch.int16))
 
 
 def test_leading_dimensions_column_slab(env):

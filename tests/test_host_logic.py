@@ -45,6 +45,13 @@ def test_gemm_generator_rules():
     assert not g.is_valid_config(200, 3, 1, 1, 8, 227 * 1024)      # N not a multiple of 64
     assert all(c[1] <= 64 for c in g.generate_configs(64))
     assert len(g.generate_configs(227, full=True)) > len(cfgs)
+    # tall tiles: two accumulators of 256 columns, 48 KiB per stage; 5 stages do not fit
+    tall = g.generate_tall_configs(227)
+    assert {(c[1], c[2]) for c in tall} == {(256, 3), (256, 4)} and {c[3] for c in tall} == set(g.TALL_BS_W_VALUES)
+    for name, bn, stages, bs_w in tall:
+        assert name == g.tall_config_name(bn, stages, bs_w) and name.startswith("bf16_bm512_")
+        assert g.tall_smem_bytes(bn, stages) <= 227 * 1024 and 2 * bn <= 512
+    assert g.tall_smem_bytes(256, 5) > 227 * 1024 and not g.generate_tall_configs(100)
 
 
 def test_gemm_generator_writes_reference_style_cmake(tmp_path):
@@ -58,8 +65,10 @@ def test_gemm_generator_writes_reference_style_cmake(tmp_path):
     assert "set(GEMM_TN_DEFAULT_CONFIG" in text
     splitk = g.generate_splitk_configs(200)
     assert inc.read_text().count("B200_GEMM_CONFIG(\"") == len(cfgs)
+    tall = g.generate_tall_configs(200)
     assert inc.read_text().count("B200_GEMM_SPLITK_CONFIG(\"") == len(splitk) == 9
-    assert reg.read_text().count("B200_GEMM_ENTRY(") == len(cfgs) + len(splitk) + 1  # + the comment line
+    assert inc.read_text().count("B200_GEMM_TALL_CONFIG(\"") == len(tall) == 3     # 4 stages need > 200 KiB
+    assert reg.read_text().count("B200_GEMM_ENTRY(") == len(cfgs) + len(splitk) + len(tall) + 1  # + the comment line
     for name, bn, stages, split_k in splitk:
         assert name == g.splitk_config_name(bn, stages, split_k) and split_k in (2, 4, 8)
         assert g.splitk_smem_bytes(bn, stages) <= 200 * 1024
@@ -107,8 +116,13 @@ def test_config_tables_match_generators(lib):
     g = _import_from(os.path.join(PKG, "gemm"), "gemm_configs")
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     gc = capi.gemm_configs()
-    assert [c["name"] for c in gc] == [c[0] for c in g.generate_configs(227) + g.generate_splitk_configs(227)]
+    assert [c["name"] for c in gc] == [c[0] for c in g.generate_configs(227) + g.generate_splitk_configs(227) +
+                                       g.generate_tall_configs(227)]
     for c in gc:
+        if c["bm"] == 512:
+            assert c["smem_bytes"] == g.tall_smem_bytes(c["bn"], c["stages"])
+            assert c["cta_group"] == 2 and c["acc_bufs"] == 2 and c["tmem_cols"] == 512 and c["bk"] == 64
+            continue
         if c["split_k"] > 1:
             assert c["smem_bytes"] == g.splitk_smem_bytes(c["bn"], c["stages"])
             assert c["name"].endswith("_splitk%d" % c["split_k"]) and c["cta_group"] == 1
@@ -129,9 +143,12 @@ def test_config_lookup(lib):
     first = lib.b200_gemm_get_config(0).contents.name
     assert lib.b200_gemm_find_config(first) == 0
     assert not lib.b200_gemm_get_config(-1) and not lib.b200_gemm_get_config(10 ** 6)
-    # 8192^3 gets a 256x256 CTA-pair tile; 512^3 a small tile that spreads over more SMs
+    # 8192^3 gets the tall 512x256 CTA-pair tile, a shape whose last wave it would leave ragged
+    # the 256x256 one; 512^3 a small tile that spreads over more SMs
     big = lib.b200_gemm_get_config(lib.b200_gemm_default_config(8192, 8192, 8192)).contents
-    assert (big.bm, big.bn, big.cta_group) == (256, 256, 2)
+    assert (big.bm, big.bn, big.cta_group, big.bs_w) == (512, 256, 2, 16)
+    mid = lib.b200_gemm_get_config(lib.b200_gemm_default_config(16384, 1792, 4096)).contents
+    assert (mid.bm, mid.bn, mid.cta_group) == (256, 256, 2)
     small = lib.b200_gemm_get_config(lib.b200_gemm_default_config(512, 512, 512)).contents
     assert small.bn == 64 and small.cta_group == 1
     ragged = lib.b200_gemm_get_config(lib.b200_gemm_default_config(100, 100, 100)).contents

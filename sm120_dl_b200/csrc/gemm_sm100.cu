@@ -38,6 +38,11 @@ constexpr int kEpiWarps = 4;
 constexpr int kEpiBoxRows = 32;
 constexpr int kEpiBoxBytes = kEpiBoxRows * 128;  // 4 KiB: 32 rows x 64 bf16
 constexpr int kThreads = 32 * (2 + kEpiWarps);
+// Tall tiles have one group of four epilogue warps per accumulator, so that both accumulators
+// of a finished tile are drained at the same time.
+// (Twelve warps: registers are handed out per warp slot of the four schedulers, so ten warps
+// would be budgeted like twelve anyway, 168 registers per thread; warps 2 and 3 idle.)
+constexpr int threads_for(int mh) { return mh == 2 ? 384 : kThreads; }
 constexpr int kMaxDst = 8;                  // copies of C one launch can write (one per GPU of a box)
 
 // Tensor maps of every destination of C.  With one entry this is the plain GEMM; with several,
@@ -61,7 +66,10 @@ struct GemmTraits {
     static constexpr int kACtaStageBytes = MH * kAStageBytes;
     static constexpr int kStageBytes = kACtaStageBytes + kBStageBytes;
     static constexpr int kRingBytes = STAGES * kStageBytes;
-    static constexpr int kEpiBytes = kEpiWarps * 2 * kEpiBoxBytes;
+    // staging boxes per epilogue warp: two (store of one overlaps the fill of the other), or one
+    // where there are twice the warps (their stores are off the critical path, see the epilogue)
+    static constexpr int kEpiBoxesPerWarp = MH == 2 ? 1 : 2;
+    static constexpr int kEpiBytes = kEpiWarps * MH * kEpiBoxesPerWarp * kEpiBoxBytes;
     static constexpr int kBarrierBytes = (2 * STAGES + 2 * ACC_BUFS) * 8 + 16;
     // +1024: the dynamic segment is only guaranteed 16-byte aligned; the ring needs 1024.
     static constexpr int kSmemBytes = kRingBytes + kEpiBytes + kBarrierBytes + 1024;
@@ -148,7 +156,7 @@ __device__ __forceinline__ bool work_item(const StreamKPlan& plan, int group, in
 }
 
 template <int BN, int STAGES, int CTA_GROUP, int ACC_BUFS, int MH>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(threads_for(MH), 1)
 gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CMapSet tmap_c, int n_dst, int M, int N, int K, int bs_w,
@@ -220,6 +228,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int group = blockIdx.x / CTA_GROUP;
     const int num_groups = gridDim.x / CTA_GROUP;
 
+    constexpr int kEpiWarp0 = (MH == 2) ? 4 : 2;   // first epilogue warp
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
@@ -285,40 +294,64 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             WorkItem item;
             for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
                 if constexpr (MH == 2) {
-                    // Both accumulators belong to this tile: accumulator h is free once the
-                    // epilogue has drained the previous tile's half h, so the first k-block's
-                    // MMAs into half 0 run while half 1 is still being drained.
+                    // Both accumulators belong to this tile and both are full at its end, so the
+                    // two halves are skewed by kSkew k-blocks at the ends of a tile only: half 0
+                    // runs its first blocks while half 1's accumulator is still being drained
+                    // (half 1 then catches up on the same ring slots), and finishes its last
+                    // blocks first so that its drain starts while half 1 is still computing.  In
+                    // between the halves move in lockstep and no ring slot is held longer than
+                    // one k-block.  (Half 0 never holds more than kSkew < STAGES slots.)
+                    constexpr int kSkew = 2;
+                    static_assert(kSkew < STAGES, "the lead of half 0 must fit in the ring");
                     const uint32_t acc_ph = local_tile & 1u;
-                    for (int kb = item.kb_begin; kb < item.kb_end; ++kb) {
-                        ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s));
-                        if (!ok) break;
-                        const bool first = (kb == item.kb_begin);
-                        const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + s * T::kACtaStageBytes);
-                        const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + s * T::kBStageBytes);
+                    const int n = item.kb_end - item.kb_begin;
+                    const int lead = (n / 2 < kSkew) ? n / 2 : kSkew;
+                    int s_back = s;   // next slot half 1 consumes (and releases); s = next slot half 0 consumes
+                    // MMAs of half h on ring slot `slot`; `first`: the accumulator is overwritten
+                    auto issue_half = [&](int h, int slot, bool first, bool release) {
+                        const uint64_t a_desc = smem_desc_kmajor_sw128(ring_a + slot * T::kACtaStageBytes + h * kAStageBytes);
+                        const uint64_t b_desc = smem_desc_kmajor_sw128(ring_b + slot * T::kBStageBytes);
+                        if (elect_one()) {
 #pragma unroll
-                        for (int h = 0; h < 2; ++h) {
-                            if (first) {
-                                ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8 * h, acc_ph ^ 1u, 0x200u + h));
-                                if (!ok) break;
+                            for (int k = 0; k < kBK / 16; ++k) {
+                                mma_ss<CTA_GROUP>(tmem_base + h * BN, a_desc + 2 * k, b_desc + 2 * k, idesc,
+                                                  (!first || k != 0) ? 1u : 0u);
                             }
-                            tc_fence_after();
-                            if (elect_one()) {
-#pragma unroll
-                                for (int k = 0; k < kBK / 16; ++k) {
-                                    mma_ss<CTA_GROUP>(tmem_base + h * BN, a_desc + (h * (kAStageBytes >> 4) + 2 * k),
-                                                      b_desc + 2 * k, idesc, (!first || k != 0) ? 1u : 0u);
-                                }
-                                if (h == 1) mma_commit<CTA_GROUP>(empty_bar + 8 * s);
-                            }
-                            __syncwarp();
+                            if (release) mma_commit<CTA_GROUP>(empty_bar + 8 * slot);
                         }
-                        if (!ok) break;
+                        __syncwarp();
+                    };
+                    auto front = [&](bool first) {   // half 0 takes the next slot once its data has landed
+                        ok = __all_sync(0xffffffffu, mbar_wait(guard, full_bar + 8 * s, ph, 0x300u + s));
+                        if (!ok) return;
+                        if (first) {
+                            ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar, acc_ph ^ 1u, 0x200u));
+                            if (!ok) return;
+                        }
+                        tc_fence_after();
+                        issue_half(0, s, first, false);
                         if (++s == STAGES) { s = 0; ph ^= 1u; }
+                    };
+                    auto back = [&](bool first) {    // half 1 follows on a slot half 0 has used, and releases it
+                        if (first) {
+                            ok = __all_sync(0xffffffffu, mbar_wait(guard, accempty_bar + 8, acc_ph ^ 1u, 0x201u));
+                            if (!ok) return;
+                            tc_fence_after();
+                        }
+                        issue_half(1, s_back, first, true);
+                        if (++s_back == STAGES) s_back = 0;
+                    };
+                    for (int kb = 0; kb < lead && ok; ++kb) front(kb == 0);
+                    for (int kb = 0; kb < lead && ok; ++kb) back(kb == 0);
+                    for (int kb = lead; kb < n - lead && ok; ++kb) {
+                        front(kb == 0);
+                        if (ok) back(kb == 0);
                     }
-                    if (ok && elect_one()) {
-                        mma_commit<CTA_GROUP>(accfull_bar);
-                        mma_commit<CTA_GROUP>(accfull_bar + 8);
-                    }
+                    for (int kb = n - lead; kb < n && ok; ++kb) front(false);
+                    if (ok && elect_one()) mma_commit<CTA_GROUP>(accfull_bar);
+                    __syncwarp();
+                    for (int kb = n - lead; kb < n && ok; ++kb) back(false);
+                    if (ok && elect_one()) mma_commit<CTA_GROUP>(accfull_bar + 8);
                     __syncwarp();
                     continue;
                 }
@@ -351,10 +384,11 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 __syncwarp();
             }
         }
-    } else {
+    } else if (warp >= kEpiWarp0) {
         // ---------------------------------------------------------------------- epilogue
         const int q = warp & 3;  // tensor-memory lane quadrant this warp may read
-        const uint32_t my_epi = epi_base + (warp - 2) * 2 * kEpiBoxBytes;
+        const uint32_t my_epi = epi_base + (warp - kEpiWarp0) * T::kEpiBoxesPerWarp * kEpiBoxBytes;
+        const int my_half = (MH == 2) ? (warp - kEpiWarp0) >> 2 : 0;   // tall tiles: the accumulator this warp drains
         const uint32_t accfull_peer = (CTA_GROUP == 2) ? mapa_cluster(accfull_bar, 1) : 0u;
         const uint32_t accempty_leader = (CTA_GROUP == 2) ? mapa_cluster(accempty_bar, 0) : accempty_bar;
         uint32_t local_tile = 0;
@@ -364,15 +398,15 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int it = 0; ok && work_item(plan, group, num_groups, num_tiles, k_blocks, it, item); ++it, ++local_tile) {
             int tm, tn;
             tile_coord(item.tile, tiles_m, tiles_n, bs_w, tm, tn);
-#pragma unroll 1
-          for (int h = 0; h < MH; ++h) {   // the tile's accumulators, drained one after the other
+          {
+            const int h = my_half;
             const uint32_t buf = (MH == 2) ? static_cast<uint32_t>(h) : local_tile % ACC_BUFS;
             const uint32_t acc_ph = (MH == 2) ? (local_tile & 1u) : ((local_tile / ACC_BUFS) & 1u);
             // a long wait (a whole mainloop): the hardware parks the warp, see mbar_wait_limit
             ok = __all_sync(0xffffffffu, mbar_wait(guard, accfull_bar + 8 * buf, acc_ph, 0x400u + buf));
             if (!ok) break;
             if constexpr (CTA_GROUP == 2) {
-                if (is_leader && warp == 2 && lane == 0) mbar_arrive_remote(accfull_peer + 8 * buf);
+                if (is_leader && ((warp - kEpiWarp0) & 3) == 0 && lane == 0) mbar_arrive_remote(accfull_peer + 8 * buf);
             }
             tc_fence_after();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
@@ -394,7 +428,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     if (units * (g + 1) / num_groups >= tile_end) break;
                 }
                 for (int g = group + 1; g <= group + n_contrib && ok; ++g) {
-                    const uint32_t* flag = plan.flags + (static_cast<size_t>(g) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - 2);
+                    const uint32_t* flag = plan.flags + (static_cast<size_t>(g) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - kEpiWarp0);
                     ok = wait_flag_warp(guard, flag, plan.epoch, 0x500u);
                 }
                 if (!ok) break;
@@ -402,27 +436,22 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if constexpr (MH == 2) {
                 // The next tile's mainloop waits for this accumulator: read and round all of it
                 // first (128 packed registers per thread), hand it back, then stage and store.
+                // (32 columns per load: 128 packed + 32 loaded registers fit the 168 of a thread)
                 uint32_t packed[BN / 64][32];
 #pragma unroll
-                for (int c = 0; c < BN / 64; ++c) {
-                    uint32_t acc0[32], acc1[32];
-                    tmem_ld_32x32b_x32(t_row + c * 64, acc0);
-                    tmem_ld_32x32b_x32(t_row + c * 64 + 32, acc1);
+                for (int c2 = 0; c2 < BN / 32; ++c2) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32b_x32(t_row + c2 * 32, acc);
                     tmem_wait_ld();
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
-                        const float a0 = __uint_as_float(acc0[2 * i]), a1 = __uint_as_float(acc0[2 * i + 1]);
-                        const float b0 = __uint_as_float(acc1[2 * i]), b1 = __uint_as_float(acc1[2 * i + 1]);
+                        const float a0 = __uint_as_float(acc[2 * i]), a1 = __uint_as_float(acc[2 * i + 1]);
                         if (is_bf16) {
                             __nv_bfloat162 v0 = __floats2bfloat162_rn(a0, a1);
-                            __nv_bfloat162 v1 = __floats2bfloat162_rn(b0, b1);
-                            packed[c][i] = *reinterpret_cast<uint32_t*>(&v0);
-                            packed[c][16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                            packed[c2 >> 1][(c2 & 1) * 16 + i] = *reinterpret_cast<uint32_t*>(&v0);
                         } else {
                             __half2 v0 = __floats2half2_rn(a0, a1);
-                            __half2 v1 = __floats2half2_rn(b0, b1);
-                            packed[c][i] = *reinterpret_cast<uint32_t*>(&v0);
-                            packed[c][16 + i] = *reinterpret_cast<uint32_t*>(&v1);
+                            packed[c2 >> 1][(c2 & 1) * 16 + i] = *reinterpret_cast<uint32_t*>(&v0);
                         }
                     }
                 }
@@ -437,8 +466,10 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 }
 #pragma unroll
                 for (int c = 0; c < BN / 64; ++c) {
-                    const uint32_t box = my_epi + (stores & 1u) * kEpiBoxBytes;
-                    if (lane == 0) tma_store_wait_read<1>();
+                    // one staging box per warp: the previous store must have read it; this is
+                    // after the hand-back, with a whole mainloop to spare
+                    const uint32_t box = my_epi;
+                    if (lane == 0) tma_store_wait_read<0>();
                     __syncwarp();
                     const uint32_t row_addr = box + lane * 128;
 #pragma unroll
@@ -493,7 +524,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tmap_a,
                         __threadfence();
                         __syncwarp();
                         if (lane == 0)
-                            st_release_gpu_u32(plan.flags + (static_cast<size_t>(group) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - 2),
+                            st_release_gpu_u32(plan.flags + (static_cast<size_t>(group) * CTA_GROUP + cta_rank) * kEpiWarps + (warp - kEpiWarp0),
                                                plan.epoch);
                     }
                     continue;
@@ -932,7 +963,7 @@ int launch_gemm(const DeviceInfo* dev, const b200_gemm_config& cfg, int M, int N
 
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(static_cast<unsigned>(groups * CTA_GROUP), 1, 1);
-    lc.blockDim = dim3(kThreads, 1, 1);
+    lc.blockDim = dim3(threads_for(MH), 1, 1);
     lc.dynamicSmemBytes = T::kSmemBytes;
     lc.stream = stream;
     cudaLaunchAttribute attr[1];

@@ -11,7 +11,9 @@ cudaProfilerStart/Stop), print one row per shape.  Flags: --binary, --best-file,
 
 Columns: the reference's SM% and DRAM% (sm__throughput / dram__throughput, % of peak
 sustained elapsed) plus what a tcgen05 kernel is judged by: tensor-pipe active %, DRAM bytes
-moved and the launch duration, from which TFLOP/s and GB/s follow.  ncu never changes the
+moved and the launch duration, from which TFLOP/s and GB/s follow, and the two counters that
+decide the clock of a tensor-bound kernel under the power cap (operand bytes delivered from L2
+to the SMs, warp instructions executed).  ncu never changes the
 GPU clocks here (--clock-control none).
 """
 
@@ -31,6 +33,9 @@ METRICS = {
     "rd": "dram__bytes_read.sum",
     "wr": "dram__bytes_write.sum",
     "ns": "gpu__time_duration.sum",
+    # what decides the clock under the power cap: operand bytes L2 -> SM and instructions issued
+    "l2sm": "l1tex__m_xbar2l1tex_read_bytes.sum",
+    "inst": "smsp__inst_executed.sum",
 }
 BEST_RE = re.compile(r"^BEST:\s*(\d+),(\d+),(\d+)\s+(\S+)")
 
@@ -73,7 +78,7 @@ def profile(binary, config, shape, warmup, out_dir):
             number = to_number(row.get(metric))
             if number is not None:
                 value = number
-        if value is not None and key in ("rd", "wr"):
+        if value is not None and key in ("rd", "wr", "l2sm"):
             unit = (units.get(metric) or "").lower()
             value *= {"byte": 1.0, "kbyte": 1e3, "mbyte": 1e6, "gbyte": 1e9}.get(unit, 1.0)
         if value is not None and key == "ns":
@@ -128,7 +133,7 @@ def main():
         ap.error("no shapes to profile")
 
     print(f"# binary: {binary}")
-    print(f"{'shape':<22} {'config':<44} {'SM %':>7} {'DRAM %':>7} {'tensor %':>9} {'us':>9} {'TFLOP/s':>9} {'DRAM GB':>8} {'GB/s':>8}")
+    print(f"{'shape':<22} {'config':<44} {'SM %':>7} {'DRAM %':>7} {'tensor %':>9} {'us':>9} {'TFLOP/s':>9} {'DRAM GB':>8} {'GB/s':>8} {'L2>SM GB':>9} {'Minst':>7}")
     for M, N, K, cfg in entries:
         tag = f"{M}x{N}x{K}"
         try:
@@ -142,7 +147,9 @@ def main():
         gb = (r["rd"] + r["wr"]) / 1e9 if r["rd"] is not None and r["wr"] is not None else None
         gbs = gb / (r["ns"] * 1e-9) if gb is not None and r["ns"] else None
         print(f"{tag:<22} {cfg:<44} {fmt(r['sm']):>7} {fmt(r['dram']):>7} {fmt(r['tensor']):>9} {fmt(us, '{:.1f}'):>9} "
-              f"{fmt(tf, '{:.1f}'):>9} {fmt(gb, '{:.3f}'):>8} {fmt(gbs, '{:.0f}'):>8}")
+              f"{fmt(tf, '{:.1f}'):>9} {fmt(gb, '{:.3f}'):>8} {fmt(gbs, '{:.0f}'):>8} "
+              f"{fmt(r['l2sm'] / 1e9 if r['l2sm'] is not None else None, '{:.2f}'):>9} "
+              f"{fmt(r['inst'] / 1e6 if r['inst'] is not None else None, '{:.1f}'):>7}")
 
 
 if __name__ == "__main__":

@@ -38,7 +38,8 @@ extern "C" {
  * clipped on store by the TMA engine; stores clip at 16-byte granularity, hence N % 8). */
 typedef struct b200_gemm_config {
     const char* name;   /* unique, e.g. "bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8"            */
-    int bm;             /* output tile rows per CTA group (128 * cta_group)                  */
+    int bm;             /* output tile rows per CTA group: 128 * cta_group, or 512 for the "tall"
+                           CTA-pair configs, whose CTAs each hold two 128-row accumulators      */
     int bn;             /* output tile columns = N of one tcgen05.mma                        */
     int bk;             /* K extent of one pipeline stage (64 elements = one 128B swizzle)   */
     int stages;         /* depth of the TMA -> MMA shared-memory ring                        */

@@ -77,13 +77,13 @@ int launch_fa_r1(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
     return B200_OK;
 }
 
-template <int D, int STAGES, int EMU>
+template <int D, int STAGES, int EMU, int TPR>
 int launch_fa_r2(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
                  void* const* o_list, int n_dst, int batch, int seq_q, int seq_k, int heads, const int64_t* qs,
                  const int64_t* ks, const int64_t* vs, const int64_t* os, float softmax_scale, int causal,
                  cudaStream_t stream) {
     using T = FaWsTraits<D, STAGES>;
-    auto kernel = fa_fwd_ws_kernel<D, STAGES, EMU>;
+    auto kernel = fa_fwd_ws_kernel<D, STAGES, EMU, TPR>;
     CUtensorMap tq, tk, tv;
     OMapSet to;
     std::memset(&to, 0, sizeof(to));
@@ -106,7 +106,7 @@ int launch_fa_r2(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
         while (grid > 1 && gcd_int(grid, q_pairs) != 1) --grid;
     }
     const float scale_log2 = softmax_scale * 1.4426950408889634f;
-    kernel<<<grid, kWsThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, n_dst, seq_q, seq_k, heads, q_pairs,
+    kernel<<<grid, ws_threads(TPR), T::kSmemBytes, stream>>>(tq, tk, tv, to, n_dst, seq_q, seq_k, heads, q_pairs,
                                                         static_cast<int>(units), scale_log2, causal ? 1 : 0,
                                                         dev->status);
     cudaError_t e = cudaGetLastError();
@@ -116,13 +116,14 @@ int launch_fa_r2(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
 
 template <int D, int STAGES, int EMU, int LAYOUT>
 constexpr FaLaunchFn fa_launcher() {
-    static_assert(LAYOUT == 1 || LAYOUT == 2, "softmax layout is 1 or 2 threads per query row");
-    if constexpr (LAYOUT == 2) return &launch_fa_r2<D, STAGES, EMU>;
+    static_assert(LAYOUT >= 1 && LAYOUT <= 3, "layouts: 1 row-thread, 2 and 3 warp-specialised with 2 and 1 softmax threads per row");
+    if constexpr (LAYOUT == 2) return &launch_fa_r2<D, STAGES, EMU, 2>;
+    else if constexpr (LAYOUT == 3) return &launch_fa_r2<D, STAGES, EMU, 1>;
     else return &launch_fa_r1<D, STAGES, EMU>;
 }
 template <int D, int STAGES, int LAYOUT>
 constexpr int fa_smem_bytes() {
-    if constexpr (LAYOUT == 2) return FaWsTraits<D, STAGES>::kSmemBytes;
+    if constexpr (LAYOUT >= 2) return FaWsTraits<D, STAGES>::kSmemBytes;
     else return FaTraits<D, STAGES>::kSmemBytes;
 }
 
@@ -133,7 +134,7 @@ struct FaEntry {
 
 #define B200_FA_CONFIG(NAME, D, STAGES, EMU, LAYOUT, BLOCK_M, BLOCK_N)                                        \
     FaEntry{b200_fa_config{NAME, D, BLOCK_M, BLOCK_N, kTileQ, kQTiles, kTileKV, STAGES,                        \
-                           (LAYOUT == 2 ? kWsThreads : kFaThreads) / 32, fa_smem_bytes<D, STAGES, LAYOUT>(),   \
+                           (LAYOUT == 2 ? ws_threads(2) : LAYOUT == 3 ? ws_threads(1) : kFaThreads) / 32, fa_smem_bytes<D, STAGES, LAYOUT>(),   \
                            LAYOUT},                                                                            \
             fa_launcher<D, STAGES, EMU, LAYOUT>()},
 

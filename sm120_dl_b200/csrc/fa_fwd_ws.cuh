@@ -1,5 +1,5 @@
-// Attention forward, layout "r2": warp-specialised load, MMA, softmax and correction
-// warpgroups in a persistent CTA.
+// Attention forward, layouts "r2" and "r3": warp-specialised load, MMA, softmax and correction
+// warpgroups in a persistent CTA (TPR = 2 or 1 softmax threads per query row).
 //
 // Same arithmetic as the reference kernel flash_atten_v3_fwd
 // (flashattention/v3_mMnNkN/flashatten_v3.hpp:390-534): scores scaled by scale*log2(e) and
@@ -16,12 +16,19 @@
 //                        at the end of a unit turns O_i / sum into fp16, stages it in shared
 //                        memory and stores it with TMA while the softmax warps already work on
 //                        the next unit
-//   warps 8-15, 16-23    softmax of query tile 0 and 1, eight warps per tile, two threads per
-//                        row: a thread reads one half (64 keys) of its row of S from tensor
-//                        memory exactly once (tensor-memory reads are the scarce resource: a
-//                        warp gets ~48 bytes per clock), the two halves exchange their maxima
-//                        through shared memory, then exp2 / row sum / fp16 P written back
-//                        over S, handed to the MMA warp in two parts
+//   warps 8-15, 16-23    TPR = 2: softmax of query tile 0 and 1, eight warps per tile, two
+//                        threads per row: a thread reads one half (64 keys) of its row of S
+//                        from tensor memory exactly once (tensor-memory reads are the scarce
+//                        resource: a warp gets ~48 bytes per clock), the two halves exchange
+//                        their maxima through shared memory, then exp2 / row sum / fp16 P
+//                        written back over S, handed to the MMA warp in two parts
+//   warps 8-11, 12-15    TPR = 1: four warps per tile, one thread per row holding all 128
+//                        scores; the row max goes to shared memory only for the row's
+//                        correction thread
+//
+// The MMA warp has one wait per hand-off: the first part of P_i is complete when the tile's
+// softmax warps AND its correction warps have arrived (the latter meaning "O_i is rescaled, or,
+// on a unit's first block, read out: it may be accumulated into").
 //
 // One unit = 256 query rows of one (batch, head).  CTAs walk the unit list with a static
 // stride; for causal problems the grid size is chosen coprime to the number of units per head
@@ -36,15 +43,21 @@
 namespace b200 {
 namespace {
 
-constexpr int kWsThreads = 768;           // 24 warps: 2 + 2 idle, 4 correction, 16 softmax
-// setmaxnreg budgets.  A CTA of 768 threads is launched with 80 registers per thread (the
-// largest multiple of 8 that fits 64 K registers); the three budgets re-divide exactly that pool.
-constexpr int kWsRegsAtLaunch = 80;
-constexpr int kWsRegsLoadMma = 56;        // warps 0-3
-constexpr int kWsRegsCorrection = 40;     // warps 4-7
-constexpr int kWsRegsSoftmax = 96;        // warps 8-23: 64 scores of a row live at once
-static_assert(kWsRegsLoadMma * 128 + kWsRegsCorrection * 128 + kWsRegsSoftmax * 512 <= kWsRegsAtLaunch * kWsThreads,
-              "setmaxnreg budgets exceed the registers the CTA is launched with");
+// TPR = softmax threads per query row.  2 (layout "r2"): 24 warps, a thread holds 64 scores.
+// 1 (layout "r3"): 16 warps, a thread holds its whole row of 128 scores, no exchange of maxima.
+constexpr int ws_threads(int tpr) { return 32 * (8 + 8 * tpr); }   // 2 + 2 idle, 4 correction, 8*TPR softmax
+// setmaxnreg budgets.  A CTA of 768 (512) threads is launched with 80 (128) registers per
+// thread, the largest multiple of 8 that fits 64 K registers; the three budgets re-divide that pool.
+constexpr int kWsRegsLoadMma = 56;                                   // warps 0-3
+template <int TPR>
+struct WsBudget {
+    static constexpr int kThreads = 32 * (8 + 8 * TPR);
+    static constexpr int kRegsAtLaunch = TPR == 2 ? 80 : 128;
+    static constexpr int kRegsCorrection = TPR == 2 ? 40 : 48;       // warps 4-7
+    static constexpr int kRegsSoftmax = TPR == 2 ? 96 : 200;         // warps 8-: 64 or 128 scores live at once
+    static_assert(kWsRegsLoadMma * 128 + kRegsCorrection * 128 + kRegsSoftmax * 256 * TPR <= kRegsAtLaunch * kThreads,
+                  "setmaxnreg budgets exceed the registers the CTA is launched with");
+};
 constexpr int kSmemLimit = 232448;        // 227 KiB
 // P of a block is handed to the MMA warp in two parts: the first after kPart0Steps 16-key steps
 // of either half of the row, the second at the end.
@@ -59,7 +72,7 @@ struct FaWsTraits {
     static_assert(D == 64 || D == 128, "head_dim must be 64 or 128");
     static constexpr int kBoxes = D / 64;
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // a Q tile, a K block or a V block
-    static constexpr int kNumBarriers = 2 + 2 * STAGES + 2 + 4 + 8 + 2 + 2 + 2 + 2;
+    static constexpr int kNumBarriers = 2 + 2 * STAGES + 2 + 4 + 8 + 2 + 2 + 2;
     // row maxima [2 block parities][2 tiles][2 halves][128] and row sums [2 tiles][2 halves][128], fp32
     static constexpr int kSmallBytes = 2 * 2 * 2 * kTileQ * 4 + 2 * 2 * kTileQ * 4 + kNumBarriers * 8 + 16;
     // tiles first (they need 1024-byte alignment for the 128-byte swizzle): Q, ring, one staging box
@@ -155,8 +168,8 @@ __device__ unsigned long long g_fa_profile[32];
 #define FA_PROF_DUMP(base) {}
 #endif
 
-template <int D, int STAGES, int EMU>
-__global__ void __launch_bounds__(kWsThreads, 1)
+template <int D, int STAGES, int EMU, int TPR>
+__global__ void __launch_bounds__(WsBudget<TPR>::kThreads, 1)
 fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ OMapSet tmap_o, int n_dst,
                  int seq_q, int seq_k, int heads, int q_pairs, int num_units, float scale_log2, int causal,
@@ -167,19 +180,20 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const uint32_t q_smem = smem_base;                                  // [2] query tiles
     const uint32_t ring_smem = q_smem + kQTiles * T::kTileBytes;        // [STAGES] K / V blocks
     const uint32_t o_smem = ring_smem + STAGES * T::kTileBytes;         // one 128 x 64 box: staging for the O stores
-    const uint32_t max_smem = o_smem + kBoxBytes;                       // [2][2][2][128] fp32 row maxima of a block
-    const uint32_t sum_smem = max_smem + 2 * 2 * 2 * kTileQ * 4;        // [2][2][128] fp32 row sums of a finished unit
-    const uint32_t bar_base = sum_smem + 2 * 2 * kTileQ * 4;
+    const uint32_t max_smem = o_smem + kBoxBytes;                       // [2][2][TPR][128] fp32 row maxima of a block
+    constexpr int kRowSlots = TPR * kTileQ;                             // one fp32 per softmax thread of a tile
+    const uint32_t sum_smem = max_smem + 2 * 2 * kRowSlots * 4;         // [2][TPR][128] fp32 row sums of a finished unit
+    const uint32_t bar_base = sum_smem + 2 * kRowSlots * 4;
     const uint32_t q_full = bar_base;                     // TMA -> MMA: the unit's Q tiles landed
     const uint32_t q_empty = q_full + 8;                  // MMA -> TMA: last S of the unit issued and complete
     const uint32_t kv_full = q_empty + 8;                 // [STAGES] TMA -> MMA
     const uint32_t kv_empty = kv_full + 8 * STAGES;       // [STAGES] MMA -> TMA
     const uint32_t s_full = kv_empty + 8 * STAGES;        // [2] MMA -> softmax: S_i ready
-    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: part h of P_i written
+    const uint32_t p_full = s_full + 16;                  // [2][2] softmax -> MMA: part h of P_i written; the first part
+                                                          // also counts the correction warps: O_i may be accumulated into
     const uint32_t max_full = p_full + 32;                // [2][4] softmax -> softmax, correction: the block's row maxima of
                                                           // one tile and lane quadrant published (the two warps that share rows)
-    const uint32_t o_ready = max_full + 64;               // [2] correction -> MMA: O_i may be accumulated into
-    const uint32_t o_final = o_ready + 16;                // [2] MMA -> correction: O_i of the unit complete
+    const uint32_t o_final = max_full + 64;               // [2] MMA -> correction: O_i of the unit complete
     const uint32_t sum_full = o_final + 16;               // [2] softmax -> correction: row sums published
     const uint32_t sum_empty = sum_full + 16;             // [2] correction -> softmax: row sums taken
     const uint32_t tmem_slot = sum_empty + 16;
@@ -198,12 +212,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(s_full + 8 * i, 1);
-            mbar_init(p_full + 16 * i, 8);       // one arrival per softmax warp of the tile
-            mbar_init(p_full + 16 * i + 8, 8);
-            for (int q = 0; q < 4; ++q) mbar_init(max_full + 32 * i + 8 * q, 2);   // the two column halves
-            mbar_init(o_ready + 8 * i, 4);       // one arrival per correction warp
+            // one arrival per softmax warp of the tile; the first part also takes one per correction
+            // warp ("O_i may be accumulated into"), so the MMA warp has one wait for both
+            mbar_init(p_full + 16 * i, 4 * TPR + 4);
+            mbar_init(p_full + 16 * i + 8, 4 * TPR);
+            for (int q = 0; q < 4; ++q) mbar_init(max_full + 32 * i + 8 * q, TPR);   // the warps that share the quadrant's rows
             mbar_init(o_final + 8 * i, 1);
-            mbar_init(sum_full + 8 * i, 8);
+            mbar_init(sum_full + 8 * i, 4 * TPR);
             mbar_init(sum_empty + 8 * i, 4);
         }
         st_shared_u32(abort_slot, 0);
@@ -270,7 +285,6 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             uint32_t ph = 0;
             uint32_t q_ph = 0;
             uint32_t p_ph[2] = {0, 0};
-            uint32_t o_ph[2] = {0, 0};
             bool ok = true;
 
             // Descriptors are built once per operand tile; a 16-element step along the head
@@ -301,7 +315,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 bool first = !accumulate;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    if (((kk & 3) < kPart0Steps) != (h == 0)) continue;
+                    const bool in_part0 = (TPR == 2) ? ((kk & 3) < kPart0Steps) : (kk < kPart0Steps);
+                    if (in_part0 != (h == 0)) continue;
                     mma_ts(tmem_base + T::kColO + i * D, tmem_base + T::kColS + i * kTileKV + kk * 8,
                            v_desc + static_cast<uint64_t>(kk * (2048 >> 4)), idesc_pv, first ? 0u : 1u);
                     first = false;
@@ -357,10 +372,6 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                     for (int i = 0; i < 2; ++i) {
                         if (!ok || j >= u.nblk[i]) continue;
                         FA_PROF(5)
-                        ok = wait(o_ready + 8 * i, o_ph[i], 0x1228u + i);
-                        if (!ok) continue;
-                        FA_PROF(2)
-                        o_ph[i] ^= 1u;
                         ok = wait(p_full + 16 * i, p_ph[i], 0x1230u + i);
                         if (!ok) continue;
                         FA_PROF(3 + i)
@@ -404,7 +415,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             FA_PROF_DUMP(0)
         }
     } else if (warp < 8) {
-        setmaxnreg_dec<kWsRegsCorrection>();
+        setmaxnreg_dec<WsBudget<TPR>::kRegsCorrection>();
         // --------------------------------------------------------------- correction warpgroup
         const int quad = warp & 3;                      // tensor-memory lane quadrant
         const int row_in_tile = quad * 32 + lane;
@@ -425,9 +436,9 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             ok = __all_sync(0xffffffffu, mbar_wait(guard, max_full + 32 * i + 8 * quad, x_ph[i] & 1u, 0x1500u + i));
             if (!ok) return;
             FA_PROF(0)
-            const uint32_t box = max_smem + (((x_ph[i] & 1u) * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
+            const uint32_t box = max_smem + (((x_ph[i] & 1u) * 2 + i) * kRowSlots + row_in_tile) * 4;
             ++x_ph[i];
-            const float block_max = fmaxf(ld_shared_f32(box), ld_shared_f32(box + kTileQ * 4));
+            const float block_max = (TPR == 2) ? fmaxf(ld_shared_f32(box), ld_shared_f32(box + kTileQ * 4)) : ld_shared_f32(box);
             if (first) m_run[i] = -INFINITY;
             const float alpha = advance_row_max(m_run[i], block_max, scale_log2);
             if (!first && __any_sync(0xffffffffu, alpha != 1.f)) {
@@ -446,7 +457,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(o_ready + 8 * i);
+            if (lane == 0) mbar_arrive(p_full + 16 * i);
         };
         if (first_unit < num_units) {
             const UnitCoord u0 = unit_coord(first_unit, q_pairs, heads, seq_q, seq_k, causal);
@@ -478,8 +489,8 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 FA_PROF(1)
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, sum_full + 8 * i, u_ph[i], 0x1510u + i));
                 if (!ok) continue;
-                const uint32_t sums = sum_smem + (i * 2 * kTileQ + row_in_tile) * 4;
-                const float l = ld_shared_f32(sums) + ld_shared_f32(sums + kTileQ * 4);
+                const uint32_t sums = sum_smem + (i * kRowSlots + row_in_tile) * 4;
+                const float l = (TPR == 2) ? ld_shared_f32(sums) + ld_shared_f32(sums + kTileQ * 4) : ld_shared_f32(sums);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sum_empty + 8 * i);
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, o_final + 8 * i, u_ph[i], 0x1518u + i));
@@ -527,11 +538,11 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (lane == 0) tma_store_wait_read<0>();   // shared memory may go; the writes finish on their own before the grid does
         if (warp == 4) FA_PROF_DUMP(24)
     } else {
-        setmaxnreg_inc<kWsRegsSoftmax>();
+        setmaxnreg_inc<WsBudget<TPR>::kRegsSoftmax>();
         // ------------------------------------------------------------------ softmax warps
-        const int i = (warp - 8) >> 3;                  // query tile of this warp
+        const int i = (warp - 8) / (4 * TPR);           // query tile of this warp
         const int quad = warp & 3;                      // tensor-memory lane quadrant
-        const int half = ((warp - 8) >> 2) & 1;         // which 64 keys of the block
+        const int half = (TPR == 2) ? ((warp - 8) >> 2) & 1 : 0;   // which 64 keys of the block (two threads per row)
         const int row_in_tile = quad * 32 + lane;
         const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + T::kColS + i * kTileKV;
         const uint32_t t_s = t_row + half * 64;         // this thread's scores
@@ -556,6 +567,59 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 if (!ok) break;
                 FA_PROF(0)
                 tc_fence_after();
+                if constexpr (TPR == 1) {
+                    // one thread per row: the whole row of 128 scores, no partner
+                    uint32_t sr[4][32];
+                    tmem_ld_32x32b_x32(t_row + 0, sr[0]);
+                    tmem_ld_32x32b_x32(t_row + 32, sr[1]);
+                    tmem_ld_32x32b_x32(t_row + 64, sr[2]);
+                    tmem_ld_32x32b_x32(t_row + 96, sr[3]);
+                    tmem_wait_ld();
+                    const int col0 = j * kTileKV;
+                    if ((col0 + kTileKV > seq_k) || (causal && (col0 + kTileKV - 1 > u.q0 + i * kTileQ))) {
+                        const int limit = causal ? min(seq_k - 1, grow) : (seq_k - 1);  // last visible key
+#pragma unroll
+                        for (int c = 0; c < 4; ++c)
+#pragma unroll
+                            for (int x = 0; x < 32; ++x)
+                                if (col0 + c * 32 + x > limit) sr[c][x] = 0xff800000u;  // -inf
+                    }
+                    float mc[4];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        mc[c] = max3(__uint_as_float(sr[c][0]), __uint_as_float(sr[c][1]), __uint_as_float(sr[c][2]));
+#pragma unroll
+                        for (int x = 3; x < 31; x += 2)
+                            mc[c] = max3(mc[c], __uint_as_float(sr[c][x]), __uint_as_float(sr[c][x + 1]));
+                        mc[c] = fmaxf(mc[c], __uint_as_float(sr[c][31]));
+                    }
+                    const float block_max = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
+                    // for the row's correction thread
+                    st_shared_f32(max_smem + ((par * 2 + i) * kRowSlots + row_in_tile) * 4, block_max);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(max_full + 32 * i + 8 * quad);
+                    const float alpha = advance_row_max(m, block_max, scale_log2);
+                    l = mul2(l, pack2(alpha, alpha));
+                    ++blocks_done;
+                    FA_PROF(1)
+                    const float nm = -((m == -INFINITY) ? 0.f : m) * scale_log2;
+                    const f32x2 nm2 = pack2(nm, nm);
+                    uint32_t pr[8];
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        exp_16<EMU>(&sr[c >> 1][(c & 1) * 16], pr, scale2, nm2, l, poly);
+                        tmem_st_32x32b_x8(t_row + 8 * c, pr);    // 16 keys -> 8 packed columns
+                        if (c == kPart0Steps - 1 || c == 7) {
+                            tmem_wait_st();
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(p_full + 16 * i + (c == 7 ? 8 : 0));
+                            if (c != 7) FA_PROF(2)
+                        }
+                    }
+                    FA_PROF(3)
+                    continue;
+                }
                 uint32_t sa[32], sb[32];
                 tmem_ld_32x32b_x32(t_s, sa);
                 tmem_ld_32x32b_x32(t_s + 32, sb);
@@ -581,7 +645,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 }
                 const float mine = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
                 // exchange with the thread that holds the other 64 keys of this row
-                const uint32_t box = max_smem + ((par * 2 + i) * 2 * kTileQ + row_in_tile) * 4;
+                const uint32_t box = max_smem + ((par * 2 + i) * kRowSlots + row_in_tile) * 4;
                 st_shared_f32(box + half * kTileQ * 4, mine);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(max_full + 32 * i + 8 * quad);
@@ -620,13 +684,13 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
                 ok = __all_sync(0xffffffffu, mbar_wait(guard, sum_empty + 8 * i, (units_done - 1) & 1u, 0x1310u + i));
                 if (!ok) break;
             }
-            st_shared_f32(sum_smem + ((i * 2 + half) * kTileQ + row_in_tile) * 4, t0 + t1);
+            st_shared_f32(sum_smem + (i * kRowSlots + half * kTileQ + row_in_tile) * 4, t0 + t1);
             __syncwarp();
             if (lane == 0) mbar_arrive(sum_full + 8 * i);
             ++units_done;
         }
         if (warp == 8) FA_PROF_DUMP(8)
-        if (warp == 16) FA_PROF_DUMP(16)
+        if (warp == 8 + 4 * TPR) FA_PROF_DUMP(16)
     }
 
     // --------------------------------------------------------------------------- teardown

@@ -8,9 +8,9 @@ of libb200dl.so.  The log is what `python -m sm120_dl_b200.build lib --force --p
 prints (and stores as sm120_dl_b200/build/build.log).  Mangled kernel names are mapped back
 to config names:
 
-    fa_fwd_ws_kernel<D, STAGES, EMU>                  -> hd{D}_..._s{STAGES}_e{EMU}_r2
+    fa_fwd_ws_kernel<D, STAGES, EMU, TPR>             -> hd{D}_..._s{STAGES}_e{EMU}_r2 (TPR 2) or _r3 (TPR 1)
     fa_fwd_kernel<D, STAGES, EMU>                     -> hd{D}_..._s{STAGES}_e{EMU}_r1
-    gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC>   -> bf16_bm{128*CTA_GROUP}_bn{BN}_bk64_s{STAGES}_cta{..}_acc{..}
+    gemm_bf16_tn_kernel<BN, STAGES, CTA_GROUP, ACC, MH> -> bf16_bm{128*CTA_GROUP*MH}_bn{BN}_bk64_s{STAGES}_cta{..}_acc{..}
                                                          (the raster width is a launch argument)
 
     python extract_resources.py [build.log] [resource.log]
@@ -29,8 +29,8 @@ DEFAULT_OUTPUT = os.path.join(PACKAGE, "build", "resource.log")
 ENTRY = re.compile(r"Compiling entry function '([^']+)'")
 FRAME = re.compile(r"(\d+) bytes stack frame, (\d+) bytes spill stores, (\d+) bytes spill loads")
 USED = re.compile(r"Used (\d+) registers")
-FA_ARGS = re.compile(r"fa_fwd(_ws)?_kernelILi(\d+)ELi(\d+)ELi(\d+)EE")
-GEMM_ARGS = re.compile(r"gemm_bf16_tn_kernelILi(\d+)ELi(\d+)ELi(\d+)ELi(\d+)EE")
+FA_ARGS = re.compile(r"fa_fwd(_ws)?_kernelILi(\d+)ELi(\d+)ELi(\d+)E(?:Li(\d+)E)?E")
+GEMM_ARGS = re.compile(r"gemm_bf16_tn_kernelILi(\d+)ELi(\d+)ELi(\d+)ELi(\d+)ELi(\d+)EE")
 
 
 def kernel_label(mangled):
@@ -41,12 +41,13 @@ def kernel_label(mangled):
             import flash_configs
         finally:
             sys.path.remove(HERE)
-        head_dim, stages, emu = (int(x) for x in m.groups()[1:])
-        return flash_configs.config_name(head_dim, stages, emu, 2 if m.group(1) else 1)
+        head_dim, stages, emu = (int(x) for x in m.groups()[1:4])
+        layout = 1 if not m.group(1) else (3 if m.group(5) == "1" else 2)
+        return flash_configs.config_name(head_dim, stages, emu, layout)
     m = GEMM_ARGS.search(mangled)
     if m:
-        bn, stages, cta_group, acc = (int(x) for x in m.groups())
-        return f"bf16_bm{128 * cta_group}_bn{bn}_bk64_s{stages}_cta{cta_group}_acc{acc}"
+        bn, stages, cta_group, acc, halves = (int(x) for x in m.groups())
+        return f"bf16_bm{128 * cta_group * halves}_bn{bn}_bk64_s{stages}_cta{cta_group}_acc{acc}"
     return mangled
 
 

@@ -16,6 +16,9 @@ with Blackwell's vocabulary instead of mma.sync warp grids:
                r2  two threads per query row (16 softmax warps), a correction warpgroup that
                    rescales O and writes the output, persistent CTAs; a 16 KiB staging box
                    for the output and 24 warps
+               r3  the same warp-specialised persistent kernel with one softmax thread per
+                   query row (8 softmax warps, 16 warps in all): no exchange of row maxima
+                   between threads, 128 scores live per thread
                r1  one thread per query row (8 softmax warps) that also rescales O; one CTA
                    per 256 query rows, 12 warps
   emu        quarters of the exponentials evaluated by a polynomial on the FMA pipe
@@ -40,12 +43,16 @@ TILE_Q = 128
 Q_TILES = 2
 TILE_KV = 128
 SEQ_GRANULARITY = 64
-LAYOUTS = (1, 2)                                     # first = default
-STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3)}
+LAYOUTS = (1, 2, 3)
+# order in which a head dimension's layouts are emitted; the first is its default (fastest
+# measured: B16 H32 S2048 D64 r3 695 / r1 670 / r2 621 TFLOP/s, B4 H32 S4096 D128 r1 1204 /
+# r3 1056 / r2 990)
+LAYOUT_ORDER = {64: (3, 1, 2), 128: (1, 3, 2)}
+STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3), (64, 3): (8, 4), (128, 3): (4,)}
 # Quarters of the exponentials evaluated by a polynomial on the FMA pipe instead of the SFU
 # (the SFU's 16 ex2 per clock are the co-bottleneck at head_dim 128, the bottleneck at 64).
 EMU_VALUES = {64: (1, 0, 2), 128: (0, 1, 2)}   # first = default (fastest measured)
-NUM_WARPS = {2: 24, 1: 12}
+NUM_WARPS = {2: 24, 1: 12, 3: 16}
 DEFAULT_MAX_SMEM_KB = 227
 SMEM_LIMIT = DEFAULT_MAX_SMEM_KB * 1024
 TMEM_COLUMNS = 512
@@ -56,11 +63,11 @@ def tile_bytes(head_dim):
 
 
 def smem_bytes(head_dim, stages, layout):
-    if layout == 2:
-        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2][4], o_ready[2],
+    if layout >= 2:
+        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2][4],
         # o_final[2], sum_full[2], sum_empty[2]; row maxima [2][2][2][128] and row sums
-        # [2][2][128] in fp32; one 128 x 64 staging box for the output
-        barriers = (2 + 2 * stages + 2 + 4 + 8 + 2 + 2 + 2 + 2) * 8 + 16
+        # [2][2][128] in fp32 (sized for two threads per row); one 128 x 64 staging box for the output
+        barriers = (2 + 2 * stages + 2 + 4 + 8 + 2 + 2 + 2) * 8 + 16
         small = 2 * 2 * 2 * TILE_Q * 4 + 2 * 2 * TILE_Q * 4 + barriers
         return (Q_TILES + stages) * tile_bytes(head_dim) + 128 * 128 + small + 1024
     barriers = (1 + 2 * stages + 2 + 4) * 8 + 16   # q_full, ring full/empty, s_full[2], p_full[2][2]
@@ -90,7 +97,7 @@ def generate_configs(max_smem_kb, only=None):
     max_smem = max_smem_kb * 1024
     configs = []
     for head_dim in HEAD_DIMS:
-        for layout in LAYOUTS:
+        for layout in LAYOUT_ORDER[head_dim]:
             stage_values = STAGE_VALUES[(head_dim, layout)]
             for stages in stage_values:
                 if not is_valid_config(head_dim, stages, layout, max_smem):

@@ -79,8 +79,12 @@ def test_flash_generator_rules(monkeypatch, tmp_path):
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     cfgs = f.generate_configs(227)
     assert {c[1] for c in cfgs} == {64, 128}
-    assert {c[4] for c in cfgs} == {1, 2}              # both softmax layouts for every head_dim
-    assert {(c[1], c[4]) for c in cfgs} == {(64, 1), (64, 2), (128, 1), (128, 2)}
+    assert {c[4] for c in cfgs} == {1, 2, 3}           # every softmax layout for every head_dim
+    assert {(c[1], c[4]) for c in cfgs} == {(hd, r) for hd in (64, 128) for r in (1, 2, 3)}
+    firsts = {}
+    for c in cfgs:
+        firsts.setdefault(c[1], c[4])
+    assert firsts == {64: 3, 128: 1}                   # the defaults: fastest measured per head_dim
     for name, hd, stages, emu, layout, bm, bn in cfgs:
         assert f.smem_bytes(hd, stages, layout) <= 227 * 1024 and f.tmem_columns(hd) <= 512 and stages >= 3
         assert 0 <= emu <= 3 and name == f.config_name(hd, stages, emu, layout)
@@ -271,12 +275,24 @@ def test_extract_resources_maps_kernels_to_config_names(tmp_path):
         "ptxas info    : Function properties for x\n"
         "    8 bytes stack frame, 4 bytes spill stores, 12 bytes spill loads\n"
         "ptxas info    : Used 168 registers, used 16 barriers\n"
-        "ptxas info    : Compiling entry function '_ZN4b20019gemm_bf16_tn_kernelILi256ELi6ELi2ELi2EEEvi' for 'sm_100a'\n"
+        "ptxas info    : Compiling entry function '_ZN4b20019gemm_bf16_tn_kernelILi256ELi6ELi2ELi2ELi1EEEvi' for 'sm_100a'\n"
         "    0 bytes stack frame, 0 bytes spill stores, 0 bytes spill loads\n"
-        "ptxas info    : Used 96 registers\n")
+        "ptxas info    : Used 96 registers\n"
+        "ptxas info    : Compiling entry function '_ZN4b20019gemm_bf16_tn_kernelILi256ELi4ELi2ELi2ELi2EEEvi' for 'sm_100a'\n"
+        "    8 bytes stack frame, 4 bytes spill stores, 4 bytes spill loads\n"
+        "ptxas info    : Used 168 registers\n"
+        "ptxas info    : Compiling entry function '_ZN4b20016fa_fwd_ws_kernelILi64ELi8ELi1ELi1EEEvPj' for 'sm_100a'\n"
+        "    40 bytes stack frame, 60 bytes spill stores, 88 bytes spill loads\n"
+        "ptxas info    : Used 128 registers\n"
+        "ptxas info    : Compiling entry function '_ZN4b20016fa_fwd_ws_kernelILi128ELi4ELi0ELi2EEEvPj' for 'sm_100a'\n"
+        "    24 bytes stack frame, 40 bytes spill stores, 68 bytes spill loads\n"
+        "ptxas info    : Used 80 registers\n")
     out = tmp_path / "resource.log"
     assert mod.main([str(log), str(out)]) == 0
     lines = out.read_text().splitlines()
     assert lines[0] == "func_name spill stack registers"
     assert lines[1] == "hd128_bm64_bn64_tq128x2_tk128_s5_e0_r1 16 8 168"
     assert lines[2] == "bf16_bm256_bn256_bk64_s6_cta2_acc2 0 0 96"
+    assert lines[3] == "bf16_bm512_bn256_bk64_s4_cta2_acc2 8 8 168"
+    assert lines[4] == "hd64_bm64_bn64_tq128x2_tk128_s8_e1_r3 148 40 128"
+    assert lines[5] == "hd128_bm64_bn64_tq128x2_tk128_s4_e0_r2 108 24 80"

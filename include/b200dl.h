@@ -152,9 +152,10 @@ typedef struct b200_fa_config {
     int stages;         /* depth of the K/V shared-memory ring                               */
     int nwarps;         /* warps per CTA                                                     */
     int smem_bytes;     /* dynamic shared memory per CTA                                     */
-    int softmax_layout; /* threads sharing one query row in the softmax: 2 = with a correction
-                           warpgroup and persistent CTAs, 1 = one thread per row that also
-                           rescales O, one CTA per 256 query rows                            */
+    int softmax_layout; /* kernel layout (the trailing _r<n> of the name): 1 = one softmax thread
+                           per row that also rescales O, one CTA per 256 query rows; 2 = load,
+                           MMA, softmax and correction warpgroups in persistent CTAs, two
+                           softmax threads per row; 3 = the same with one softmax thread per row */
 } b200_fa_config;
 
 int b200_fa_num_configs(void);

@@ -278,7 +278,8 @@ def test_fp16_operands(env):
     b_h = rng.uniform(-1, 1, size=(N, K)).astype(np.float16)
     ref = a_h.astype(np.float64) @ b_h.astype(np.float64).T
     a, b = torch.from_numpy(a_h).to(dev), torch.from_numpy(b_h).to(dev)
-    for cfg in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn128_bk64_s6_cta1_acc2_bsw8"):
+    for cfg in ("bf16_bm256_bn256_bk64_s6_cta2_acc2_bsw8", "bf16_bm128_bn128_bk64_s6_cta1_acc2_bsw8",
+                "bf16_bm512_bn256_bk64_s4_cta2_acc2_bsw16"):
         c = ops.gemm_f16_tn(a, b, config=cfg)
         assert capi.device_status() == 0
         st = oracle.compare(c.float().cpu().numpy(), ref, 1e-2, 5e-2)

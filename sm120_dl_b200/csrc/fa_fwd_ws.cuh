@@ -48,14 +48,17 @@ namespace {
 constexpr int ws_threads(int tpr) { return 32 * (8 + 8 * tpr); }   // 2 + 2 idle, 4 correction, 8*TPR softmax
 // setmaxnreg budgets.  A CTA of 768 (512) threads is launched with 80 (128) registers per
 // thread, the largest multiple of 8 that fits 64 K registers; the three budgets re-divide that pool.
-constexpr int kWsRegsLoadMma = 56;                                   // warps 0-3
-template <int TPR>
+template <int TPR, int D>
 struct WsBudget {
     static constexpr int kThreads = 32 * (8 + 8 * TPR);
     static constexpr int kRegsAtLaunch = TPR == 2 ? 80 : 128;
-    static constexpr int kRegsCorrection = TPR == 2 ? 40 : 48;       // warps 4-7
-    static constexpr int kRegsSoftmax = TPR == 2 ? 96 : 200;         // warps 8-: 64 or 128 scores live at once
-    static_assert(kWsRegsLoadMma * 128 + kRegsCorrection * 128 + kRegsSoftmax * 256 * TPR <= kRegsAtLaunch * kThreads,
+    // TPR = 1, measured (B4 H32 S4096 D128 / B16 H32 S2048 D64, TFLOP/s): 56/48/200 1018-1056 / 686-695,
+    // 80/40/192 1050-1102 / 611 -- at head_dim 128 the MMA warp spills below ~80 registers (its
+    // instruction stream is the serial resource of the loop), at 64 the larger budget only costs
+    static constexpr int kRegsLoadMma = TPR == 2 ? 56 : (D == 128 ? 80 : 56);   // warps 0-3
+    static constexpr int kRegsCorrection = TPR == 2 ? 40 : (D == 128 ? 40 : 48);   // warps 4-7
+    static constexpr int kRegsSoftmax = TPR == 2 ? 96 : (D == 128 ? 192 : 200);    // warps 8-: 64 or 128 scores live at once
+    static_assert(kRegsLoadMma * 128 + kRegsCorrection * 128 + kRegsSoftmax * 256 * TPR <= kRegsAtLaunch * kThreads,
                   "setmaxnreg budgets exceed the registers the CTA is launched with");
 };
 constexpr int kSmemLimit = 232448;        // 227 KiB
@@ -169,7 +172,7 @@ __device__ unsigned long long g_fa_profile[32];
 #endif
 
 template <int D, int STAGES, int EMU, int TPR>
-__global__ void __launch_bounds__(WsBudget<TPR>::kThreads, 1)
+__global__ void __launch_bounds__(WsBudget<TPR, D>::kThreads, 1)
 fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ OMapSet tmap_o, int n_dst,
                  int seq_q, int seq_k, int heads, int q_pairs, int num_units, float scale_log2, int causal,
@@ -240,7 +243,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     const int unit_stride = static_cast<int>(gridDim.x);
 
     if (warp < 4) {
-        setmaxnreg_dec<kWsRegsLoadMma>();
+        setmaxnreg_dec<WsBudget<TPR, D>::kRegsLoadMma>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- TMA producer
             int s = 0;
@@ -415,7 +418,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
             FA_PROF_DUMP(0)
         }
     } else if (warp < 8) {
-        setmaxnreg_dec<WsBudget<TPR>::kRegsCorrection>();
+        setmaxnreg_dec<WsBudget<TPR, D>::kRegsCorrection>();
         // --------------------------------------------------------------- correction warpgroup
         const int quad = warp & 3;                      // tensor-memory lane quadrant
         const int row_in_tile = quad * 32 + lane;
@@ -538,7 +541,7 @@ fa_fwd_ws_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
         if (lane == 0) tma_store_wait_read<0>();   // shared memory may go; the writes finish on their own before the grid does
         if (warp == 4) FA_PROF_DUMP(24)
     } else {
-        setmaxnreg_inc<WsBudget<TPR>::kRegsSoftmax>();
+        setmaxnreg_inc<WsBudget<TPR, D>::kRegsSoftmax>();
         // ------------------------------------------------------------------ softmax warps
         const int i = (warp - 8) / (4 * TPR);           // query tile of this warp
         const int quad = warp & 3;                      // tensor-memory lane quadrant

@@ -473,10 +473,11 @@ def config5_leg(bench, args):
             rec = sweep.run_gemm(*shape, bench.world, bench.rank, bench.dev, iterations)
         else:
             rec = sweep.run_attention(bench.world, bench.rank, bench.dev, iterations)
-        n_variants = 1 + (rec["gather_ms"] is not None) + (rec["fused_ms"] is not None)
+        panel = rec.get("panel_gather_ms")
+        n_variants = 1 + (rec["gather_ms"] is not None) + (rec["fused_ms"] is not None) + 4 * (panel is not None)
         bench.launches += n_variants * iterations
-        compute_ms, gather_ms, fused_ms = bench.max_over_ranks(
-            rec["compute_ms"], rec["gather_ms"] or 0.0, rec["fused_ms"] or 0.0)
+        compute_ms, gather_ms, fused_ms, panel_ms = bench.max_over_ranks(
+            rec["compute_ms"], rec["gather_ms"] or 0.0, rec["fused_ms"] or 0.0, panel or 0.0)
         rate = lambda ms: rec["flops"] / (ms * 1e-3) / 1e12 if ms > 0 else None  # noqa: E731
         records.append({
             "workload": rec["workload"], "scaling": "strong", "n_gpus": bench.world, "iterations": iterations,
@@ -484,6 +485,7 @@ def config5_leg(bench, args):
             "compute_ms": compute_ms, "tflops": rate(compute_ms),
             "frac_of_nominal_2250_per_gpu": rate(compute_ms) / bench.world / NOMINAL_TFLOPS,
             "nccl_gather_ms": gather_ms or None, "tflops_nccl_gather": rate(gather_ms),
+            "nccl_gather_4_row_panels_ms": panel_ms or None,
             "fused_gather_ms": fused_ms or None, "tflops_fused_gather": rate(fused_ms)})
         bench.torch.cuda.empty_cache()
     assert capi.device_status() == 0, "a kernel reported a timed-out wait"

@@ -44,7 +44,7 @@ def _world(group):
 
 
 def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None, config=None, out=None,
-                      root=None):
+                      root=None, panels=1):
     """C = A @ B^T with the N dimension split across the ranks of `group`.
 
     a [M,K] is replicated; b is the FULL [N,K] matrix on every rank (each rank reads only
@@ -56,7 +56,10 @@ def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None,
     finished tile straight into the ranks' copies of c_full over NVLink (see
     gemm_column_shard_fused; `root` limits the destinations to one rank).  Without such a
     buffer it falls back to an NCCL all-gather of the slabs plus a strided copy into place
-    (column slabs of a row-major matrix are not contiguous).
+    (column slabs of a row-major matrix are not contiguous).  With panels > 1 that fallback is
+    pipelined over row panels of A: the slab of panel p is gathered (asynchronously, on the
+    collective's own stream) while the GEMM of panel p+1 runs, so the collective hides the
+    compute instead of following it.  (Equal shards only; M must divide into the panels.)
     """
     if gather and out is not None and compute is None:
         c_full, handle = out
@@ -69,12 +72,26 @@ def gemm_column_shard(a, b, group=None, gather=False, granule=256, compute=None,
     N = b.shape[0]
     n0, n1 = shard_bounds(N, world, rank, granule)
     slab = torch.empty((M, n1 - n0), dtype=a.dtype, device=a.device)
+    sizes = [shard_bounds(N, world, r, granule) for r in range(world)]
+    widths = [e - s for s, e in sizes]
+    if gather and world > 1 and panels > 1 and len(set(widths)) == 1 and widths[0] > 0 and M % panels == 0:
+        rows = M // panels
+        full = torch.empty((M, N), dtype=a.dtype, device=a.device)
+        staging = torch.empty((panels, world, rows, widths[0]), dtype=a.dtype, device=a.device)
+        pending = []
+        for p in range(panels):
+            part = slab[p * rows:(p + 1) * rows]                     # contiguous: whole rows of the slab
+            compute(a[p * rows:(p + 1) * rows], b[n0:n1], part)
+            pending.append(dist.all_gather_into_tensor(staging[p].view(world * rows, widths[0]), part, group=group,
+                                                       async_op=True))
+        for p, work in enumerate(pending):
+            work.wait()
+            full[p * rows:(p + 1) * rows].view(rows, world, widths[0]).copy_(staging[p].permute(1, 0, 2))
+        return full, (n0, n1)
     if n1 > n0:
         compute(a, b[n0:n1], slab)
     if not gather or world == 1:
         return slab, (n0, n1)
-    sizes = [shard_bounds(N, world, r, granule) for r in range(world)]
-    widths = [e - s for s, e in sizes]
     full = torch.empty((M, N), dtype=a.dtype, device=a.device)
     if len(set(widths)) == 1:
         staging = torch.empty((world, M, widths[0]), dtype=a.dtype, device=a.device)

@@ -69,6 +69,14 @@ def run_gemm(M, N, K, world, rank, dev, iterations):
         gather_ms = timed(lambda: sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg), iterations)
         full, _ = sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg)
         assert torch.equal(full[:, n0:n1].view(torch.int16), slab.view(torch.int16)), "gathered C differs from the shard"
+    # the same all-gather pipelined over four row panels of A (gather of panel p under the GEMM of p+1)
+    panel_ms = None
+    if world > 1 and M % 4 == 0:
+        panel_ms = timed(lambda: sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg, panels=4),
+                         iterations)
+        piped, _ = sharded.gemm_column_shard(a, b, gather=True, granule=256, config=cfg, panels=4)
+        assert torch.equal(piped.view(torch.int16), full.view(torch.int16)), "pipelined gather differs from the plain one"
+        del piped
     fused_ms = None
     if world > 1:
         c_sym, handle = sharded.symmetric_empty((M, N), torch.bfloat16, dev)
@@ -84,7 +92,7 @@ def run_gemm(M, N, K, world, rank, dev, iterations):
     flops = 2.0 * M * N * K
     return {"workload": f"gemm_bf16 M={M} N={N} K={K}", "flops": flops, "kernel_config": capi.gemm_configs()[cfg]["name"],
             "shard": f"columns [{n0},{n1}) of {N}", "compute_ms": compute_ms, "gather_ms": gather_ms,
-            "fused_ms": fused_ms}
+            "panel_gather_ms": panel_ms, "fused_ms": fused_ms}
 
 
 def run_attention(world, rank, dev, iterations):

@@ -227,6 +227,10 @@ assert slab.shape == (64, n1 - n0) and torch.allclose(slab, (a @ b.T)[:, n0:n1],
 b2 = torch.randn(512, 32)
 full2, _ = sharded.gemm_column_shard(a, b2, gather=True, granule=256, compute=mm)
 assert torch.allclose(full2, a @ b2.T, atol=1e-5), "even gather"
+full3, _ = sharded.gemm_column_shard(a, b2, gather=True, granule=256, compute=mm, panels=4)
+assert torch.equal(full3, full2), "row-panel pipelined gather"
+full4, _ = sharded.gemm_column_shard(a, b, gather=True, granule=256, compute=mm, panels=4)   # uneven: plain path
+assert torch.allclose(full4, a @ b.T, atol=1e-5), "uneven shards ignore panels"
 q = torch.randn(2, 16, 6, 8); k = torch.randn(2, 16, 6, 8); v = torch.randn(2, 16, 6, 8)
 def attn(x, y, z, causal):
     o = torch.nn.functional.scaled_dot_product_attention(x.permute(0, 2, 1, 3), y.permute(0, 2, 1, 3),

@@ -1225,7 +1225,9 @@ int b200_gemm_default_config(int M, int N, int K) {
         // (measured: 8192^3 +7 %, K = 4096 shapes +1-3 %); their epilogue overlaps less.
         const int halves = c.bm / (128 * c.cta_group);
         if (halves == 2) t_kb *= 2.0 * 0.97;
-        if (ctas < sms || c.split_k > 1) {
+        // (only where the operands do not sit in L2: 2048^3 reads its 16 MB from L2 at more than that)
+        const double operand_mb = 2.0 * (static_cast<double>(M) + N) * K / 1e6;
+        if ((ctas < sms || c.split_k > 1) && operand_mb > 64.0) {
             const double bytes = (128.0 + c.bn / c.cta_group) * 128.0;                 // A and B rows of one k-block
             const double gbs = 95.0 < 11500.0 / active ? 95.0 : 11500.0 / active;       // per CTA
             const double t_mem = bytes / (gbs * 1e3);
@@ -1237,7 +1239,8 @@ int b200_gemm_default_config(int M, int N, int K) {
                                            : (halves == 2 ? 4.0 + 0.8 * (waves - 1)
                                               : c.acc_bufs > 1 ? 4.0 : 4.0 + 1.5 * (waves - 1)) +
                                                  // the pair handshake per tile shows on latency-bound problems
-                                                 ((c.cta_group == 2 && tiles < sms / 2) ? 1.0 : 0.0);
+                                                 // (2048^3: 64 pair tiles 18.7 us, 128 single-CTA tiles 16.7 us)
+                                                 ((c.cta_group == 2 && tiles < sms / 2) ? 2.5 : 0.0);
         double cost = waves * kb_per_cta * t_kb + fixed;
         // ties: deeper ring; strip width 8 (16 for tall tiles), fastest measured on 8192^3
         cost *= 1.0 - 0.0005 * c.stages - (c.bs_w == (halves == 2 ? 16 : 8) ? 0.0002 : 0.0);

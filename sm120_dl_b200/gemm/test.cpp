@@ -31,6 +31,7 @@
 #include <cuda_profiler_api.h>
 #include <unistd.h>
 
+#include "b200dl.h"
 #include "gemm_config_registry.hpp"
 
 namespace {
@@ -414,6 +415,31 @@ ShapeBenchmark benchmark_all_configs_for_shape(const GemmShape& shape) {
     if (!rows.empty() && rows.front().result.ok) {
         out.best = rows.front().config;
         out.best_result = rows.front().result;
+        // How the config the library picks by itself for this shape (b200_gemm_default_config:
+        // a cost model, no measurement) compares with the measured best.  Not in the reference.
+        // The ranking above times the configs one after the other, so a config's place in that
+        // order (how warm and how power-capped the GPU is by then) colours its figure by several
+        // percent; the two configs compared here are therefore re-timed alternately.
+        const int chosen = b200_gemm_default_config(shape.M, shape.N, shape.K);
+        if (chosen >= 0 && static_cast<size_t>(chosen) < kGemmConfigCount) {
+            const GemmConfig& def = kGemmConfigs[chosen];
+            if (&def == out.best) {
+                std::printf("DEFAULT: %d,%d,%d %s is the best config\n", shape.M, shape.N, shape.K, def.name);
+            } else if (config_supports_problem(def, shape.M, shape.N, shape.K)) {
+                double t_def = 0.0, t_best = 0.0, ms_def = 0.0;
+                bool both_ok = true;
+                for (int round = 0; round < 2 && both_ok; ++round) {
+                    const BenchmarkResult a = benchmark_config(def, problem);
+                    const BenchmarkResult b = benchmark_config(*out.best, problem);
+                    both_ok = a.ok && b.ok;
+                    if (a.throughput > t_def) { t_def = a.throughput; ms_def = a.latency_ms; }
+                    if (b.throughput > t_best) t_best = b.throughput;
+                }
+                if (both_ok)
+                    std::printf("DEFAULT: %d,%d,%d %s   %.4f ms %.3f TFLOP/s = %.2f%% of %s re-timed alternately\n", shape.M,
+                                shape.N, shape.K, def.name, ms_def, t_def, percent_of(t_def, t_best), out.best->name);
+            }
+        }
     }
     return out;
 }

@@ -16,6 +16,7 @@
 #include <cstring>
 
 #include "fa_fwd_rowthread.cuh"
+#include "fa_fwd_rowthread_persistent.cuh"
 #include "fa_fwd_ws.cuh"
 #include "runtime.h"
 
@@ -114,16 +115,56 @@ int launch_fa_r2(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
     return B200_OK;
 }
 
+// Layout r4: the row-thread kernel with persistent CTAs.
+template <int D, int STAGES, int EMU>
+int launch_fa_r4(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q, const void* k, const void* v,
+                 void* const* o_list, int n_dst, int batch, int seq_q, int seq_k, int heads, const int64_t* qs,
+                 const int64_t* ks, const int64_t* vs, const int64_t* os, float softmax_scale, int causal,
+                 cudaStream_t stream) {
+    using T = FaPersTraits<D, STAGES>;
+    auto kernel = fa_fwd_pers_kernel<D, STAGES, EMU>;
+    CUtensorMap tq, tk, tv;
+    OMapSet to;
+    std::memset(&to, 0, sizeof(to));
+    if (int rc = make_tmap(&tq, q, batch, seq_q, heads, D, qs, 128)) return rc;
+    if (int rc = make_tmap(&tk, k, batch, seq_k, heads, D, ks, 128)) return rc;
+    if (int rc = make_tmap(&tv, v, batch, seq_k, heads, D, vs, 128)) return rc;
+    for (int d = 0; d < n_dst; ++d) {
+        if (int rc = make_tmap(&to.m[d], o_list[d], batch, seq_q, heads, D, os, 128)) return rc;
+    }
+    static bool attr_done[kMaxDevices] = {};
+    if (int rc = set_smem_once(kernel, T::kSmemBytes, dev->device, attr_done, cfg.name)) return rc;
+    const int q_pairs = (seq_q + kQTiles * kTileQ - 1) / (kQTiles * kTileQ);
+    const long units = static_cast<long>(q_pairs) * heads * batch;
+    if (units > 0x7fffffffL) return fail(B200_ESHAPE, "too many work units");
+    int grid = dev->sm_count < units ? dev->sm_count : static_cast<int>(units);
+    if (causal && units > grid) {
+        // heaviest units of a head first, every grid-th unit per CTA: a grid coprime to the
+        // units per head gives every CTA every weight class equally often
+        while (grid > 1 && gcd_int(grid, q_pairs) != 1) --grid;
+    }
+    const float scale_log2 = softmax_scale * 1.4426950408889634f;
+    kernel<<<grid, kFaThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, n_dst, seq_q, seq_k, heads, q_pairs,
+                                                        static_cast<int>(units), scale_log2, causal ? 1 : 0,
+                                                        dev->status);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
+    return B200_OK;
+}
+
 template <int D, int STAGES, int EMU, int LAYOUT>
 constexpr FaLaunchFn fa_launcher() {
-    static_assert(LAYOUT >= 1 && LAYOUT <= 3, "layouts: 1 row-thread, 2 and 3 warp-specialised with 2 and 1 softmax threads per row");
+    static_assert(LAYOUT >= 1 && LAYOUT <= 4,
+                  "layouts: 1 row-thread, 2 and 3 warp-specialised with 2 and 1 softmax threads per row, 4 persistent row-thread");
     if constexpr (LAYOUT == 2) return &launch_fa_r2<D, STAGES, EMU, 2>;
     else if constexpr (LAYOUT == 3) return &launch_fa_r2<D, STAGES, EMU, 1>;
+    else if constexpr (LAYOUT == 4) return &launch_fa_r4<D, STAGES, EMU>;
     else return &launch_fa_r1<D, STAGES, EMU>;
 }
 template <int D, int STAGES, int LAYOUT>
 constexpr int fa_smem_bytes() {
-    if constexpr (LAYOUT >= 2) return FaWsTraits<D, STAGES>::kSmemBytes;
+    if constexpr (LAYOUT == 4) return FaPersTraits<D, STAGES>::kSmemBytes;
+    else if constexpr (LAYOUT >= 2) return FaWsTraits<D, STAGES>::kSmemBytes;
     else return FaTraits<D, STAGES>::kSmemBytes;
 }
 

@@ -92,35 +92,6 @@ __device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
     return r;
 }
 
-// (pair of the head, head, batch) of unit `id`, and the key blocks its two tiles visit.
-struct UnitCoord {
-    int q0, head, batch;
-    int nblk[2];
-    int nmax;
-};
-__device__ __forceinline__ UnitCoord unit_coord(int id, int q_pairs, int heads, int seq_q, int seq_k, int causal) {
-    UnitCoord u;
-    const int hb = id / q_pairs;
-    const int p = id - hb * q_pairs;
-    const int pair = causal ? (q_pairs - 1 - p) : p;   // heaviest causal units of a head first
-    u.batch = hb / heads;
-    u.head = hb - u.batch * heads;
-    u.q0 = pair * (kQTiles * kTileQ);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        const int row0 = u.q0 + i * kTileQ;
-        if (row0 >= seq_q) {
-            u.nblk[i] = 0;
-        } else {
-            const int last_row = min(row0 + kTileQ, seq_q) - 1;
-            const int visible = causal ? min(seq_k, last_row + 1) : seq_k;
-            u.nblk[i] = (visible + kTileKV - 1) / kTileKV;
-        }
-    }
-    u.nmax = max(u.nblk[0], u.nblk[1]);
-    return u;
-}
-
 // The running max a row's accumulators are scaled to moves only when the new maximum exceeds it
 // by more than 2^kRescaleLog2 (always on the first block).  Softmax and correction threads run
 // this same function on the same inputs, so they agree bit for bit.  Returns the factor

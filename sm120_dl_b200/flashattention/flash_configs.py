@@ -19,6 +19,9 @@ with Blackwell's vocabulary instead of mma.sync warp grids:
                r3  the same warp-specialised persistent kernel with one softmax thread per
                    query row (8 softmax warps, 16 warps in all): no exchange of row maxima
                    between threads, 128 scores live per thread
+               r4  r1 with persistent CTAs: barriers and tensor memory set up once per CTA, the
+                   next unit's Q / K / V loads and first S issued under the current unit's
+                   epilogue; a 16 KiB staging box per query tile for the output
                r1  one thread per query row (8 softmax warps) that also rescales O; one CTA
                    per 256 query rows, 12 warps
   emu        quarters of the exponentials evaluated by a polynomial on the FMA pipe
@@ -43,16 +46,17 @@ TILE_Q = 128
 Q_TILES = 2
 TILE_KV = 128
 SEQ_GRANULARITY = 64
-LAYOUTS = (1, 2, 3)
+LAYOUTS = (1, 2, 3, 4)
 # order in which a head dimension's layouts are emitted; the first is its default (fastest
-# measured: B16 H32 S2048 D64 r3 695 / r1 670 / r2 621 TFLOP/s, B4 H32 S4096 D128 r1 1204 /
-# r3 1056 / r2 990)
-LAYOUT_ORDER = {64: (3, 1, 2), 128: (1, 3, 2)}
-STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3), (64, 3): (8, 4), (128, 3): (4,)}
+# measured, 50-launch runs: B4 H32 S4096 D128 r4 1231-1234 / r1 1205-1212 / r3 1050-1100 /
+# r2 ~990 TFLOP/s; B16 H32 S2048 D64 r4 740 / r3 710 / r1 661-670 / r2 ~620)
+LAYOUT_ORDER = {64: (4, 3, 1, 2), 128: (4, 1, 3, 2)}
+STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3), (64, 3): (8, 4), (128, 3): (4,),
+                (64, 4): (8, 4), (128, 4): (4, 3)}
 # Quarters of the exponentials evaluated by a polynomial on the FMA pipe instead of the SFU
 # (the SFU's 16 ex2 per clock are the co-bottleneck at head_dim 128, the bottleneck at 64).
 EMU_VALUES = {64: (1, 0, 2), 128: (0, 1, 2)}   # first = default (fastest measured)
-NUM_WARPS = {2: 24, 1: 12, 3: 16}
+NUM_WARPS = {2: 24, 1: 12, 3: 16, 4: 12}
 DEFAULT_MAX_SMEM_KB = 227
 SMEM_LIMIT = DEFAULT_MAX_SMEM_KB * 1024
 TMEM_COLUMNS = 512
@@ -63,6 +67,11 @@ def tile_bytes(head_dim):
 
 
 def smem_bytes(head_dim, stages, layout):
+    if layout == 4:
+        # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], o_final[2]; one 128 x 64
+        # staging box per query tile
+        barriers = (2 + 2 * stages + 2 + 4 + 2) * 8 + 16
+        return (Q_TILES + stages) * tile_bytes(head_dim) + Q_TILES * 128 * 128 + barriers + 1024
     if layout >= 2:
         # q_full, q_empty, ring full/empty, s_full[2], p_full[2][2], max_full[2][4],
         # o_final[2], sum_full[2], sum_empty[2]; row maxima [2][2][2][128] and row sums

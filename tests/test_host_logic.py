@@ -79,12 +79,12 @@ def test_flash_generator_rules(monkeypatch, tmp_path):
     f = _import_from(os.path.join(PKG, "flashattention"), "flash_configs")
     cfgs = f.generate_configs(227)
     assert {c[1] for c in cfgs} == {64, 128}
-    assert {c[4] for c in cfgs} == {1, 2, 3}           # every softmax layout for every head_dim
-    assert {(c[1], c[4]) for c in cfgs} == {(hd, r) for hd in (64, 128) for r in (1, 2, 3)}
+    assert {c[4] for c in cfgs} == {1, 2, 3, 4}        # every layout for every head_dim
+    assert {(c[1], c[4]) for c in cfgs} == {(hd, r) for hd in (64, 128) for r in (1, 2, 3, 4)}
     firsts = {}
     for c in cfgs:
         firsts.setdefault(c[1], c[4])
-    assert firsts == {64: 3, 128: 1}                   # the defaults: fastest measured per head_dim
+    assert firsts == {64: 4, 128: 4}                   # the defaults: fastest measured per head_dim
     for name, hd, stages, emu, layout, bm, bn in cfgs:
         assert f.smem_bytes(hd, stages, layout) <= 227 * 1024 and f.tmem_columns(hd) <= 512 and stages >= 3
         assert 0 <= emu <= 3 and name == f.config_name(hd, stages, emu, layout)

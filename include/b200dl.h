@@ -155,7 +155,8 @@ typedef struct b200_fa_config {
     int softmax_layout; /* kernel layout (the trailing _r<n> of the name): 1 = one softmax thread
                            per row that also rescales O, one CTA per 256 query rows; 2 = load,
                            MMA, softmax and correction warpgroups in persistent CTAs, two
-                           softmax threads per row; 3 = the same with one softmax thread per row */
+                           softmax threads per row; 3 = the same with one softmax thread per row;
+                           4 = layout 1 with persistent CTAs (the default)                     */
 } b200_fa_config;
 
 int b200_fa_num_configs(void);

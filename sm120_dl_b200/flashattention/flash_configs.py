@@ -52,7 +52,7 @@ LAYOUTS = (1, 2, 3, 4)
 # r2 ~990 TFLOP/s; B16 H32 S2048 D64 r4 740 / r3 710 / r1 661-670 / r2 ~620)
 LAYOUT_ORDER = {64: (4, 3, 1, 2), 128: (4, 1, 3, 2)}
 STAGE_VALUES = {(64, 2): (8, 4), (128, 2): (4,), (64, 1): (8, 4), (128, 1): (5, 3), (64, 3): (8, 4), (128, 3): (4,),
-                (64, 4): (8, 4), (128, 4): (4, 3)}
+                (64, 4): (10, 4), (128, 4): (4, 3)}
 # Quarters of the exponentials evaluated by a polynomial on the FMA pipe instead of the SFU
 # (the SFU's 16 ex2 per clock are the co-bottleneck at head_dim 128, the bottleneck at 64).
 EMU_VALUES = {64: (1, 0, 2), 128: (0, 1, 2)}   # first = default (fastest measured)

@@ -428,7 +428,7 @@ ShapeBenchmark benchmark_all_configs_for_shape(const GemmShape& shape) {
             } else if (config_supports_problem(def, shape.M, shape.N, shape.K)) {
                 double t_def = 0.0, t_best = 0.0, ms_def = 0.0;
                 bool both_ok = true;
-                for (int round = 0; round < 2 && both_ok; ++round) {
+                for (int rep = 0; rep < 2 && both_ok; ++rep) {
                     const BenchmarkResult a = benchmark_config(def, problem);
                     const BenchmarkResult b = benchmark_config(*out.best, problem);
                     both_ok = a.ok && b.ok;

@@ -10,7 +10,7 @@ cudaProfilerStart/Stop), print one row per shape.  Flags: --binary, --best-file,
 --shape M N K, --only MxNxK[,...], --warmup, --out-dir.
 
 Columns: the reference's SM% and DRAM% (sm__throughput / dram__throughput, % of peak
-sustained elapsed) plus what a tcgen05 kernel is judged by: tensor-pipe active %, DRAM bytes
+sustained elapsed) plus what tells how well a tcgen05 kernel runs: tensor-pipe active %, DRAM bytes
 moved and the launch duration, from which TFLOP/s and GB/s follow, and the two counters that
 decide the clock of a tensor-bound kernel under the power cap (operand bytes delivered from L2
 to the SMs, warp instructions executed).  ncu never changes the

@@ -128,5 +128,18 @@ __device__ __forceinline__ UnitCoord unit_coord(int id, int q_pairs, int heads, 
     return u;
 }
 
+#ifdef B200_FA_PROFILE
+// Cycle counters of CTA 0 (profiling builds only): [0..7] MMA warp, [8..15] softmax warp 8,
+// [16..23] softmax warp 16, [24..31] correction warp 4.
+__device__ unsigned long long g_fa_profile[32];
+#define FA_PROF_DECL unsigned long long prof_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned long long prof_t = clock64();
+#define FA_PROF(n) { const unsigned long long prof_now = clock64(); prof_acc[n] += prof_now - prof_t; prof_t = prof_now; }
+#define FA_PROF_DUMP(base) if (blockIdx.x == 0 && lane == 0) { for (int x = 0; x < 8; ++x) g_fa_profile[(base) + x] = prof_acc[x]; }
+#else
+#define FA_PROF_DECL
+#define FA_PROF(n) {}
+#define FA_PROF_DUMP(base) {}
+#endif
+
 }  // namespace
 }  // namespace b200

@@ -105,11 +105,23 @@ struct UnitCoord {
     int nblk[2];
     int nmax;
 };
+// Unit a persistent CTA works on in its k-th iteration, given its schedule slot
+// first + k * stride.  Normally the slot itself; with causal = 2 a CTA takes two consecutive
+// units at a time (a heavy and a light one of the same head, see unit_coord), so every CTA
+// carries the same weight whatever the sequence length.
+__device__ __forceinline__ int schedule_unit(int slot, int first, int stride, int causal) {
+    if (causal != 2) return slot;
+    const int k = (slot - first) / stride;
+    return 2 * (first + (k >> 1) * stride) + (k & 1);
+}
 __device__ __forceinline__ UnitCoord unit_coord(int id, int q_pairs, int heads, int seq_q, int seq_k, int causal) {
     UnitCoord u;
     const int hb = id / q_pairs;
     const int p = id - hb * q_pairs;
-    const int pair = causal ? (q_pairs - 1 - p) : p;   // heaviest causal units of a head first
+    // causal = 1: heaviest units of a head first.  causal = 2 (schedule_unit's pairing): heavy and
+    // light units of a head alternate (last pair, first pair, last but one, second, ...), so
+    // that two consecutive units always have the same total weight
+    const int pair = causal == 2 ? ((p & 1) ? (p >> 1) : (q_pairs - 1 - (p >> 1))) : causal ? (q_pairs - 1 - p) : p;
     u.batch = hb / heads;
     u.head = hb - u.batch * heads;
     u.q0 = pair * (kQTiles * kTileQ);

@@ -125,7 +125,9 @@ fa_fwd_pers_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
             uint32_t ph = 0;
             uint32_t q_ph = 0;
             bool ok = true;
-            for (int id = first_unit; id < num_units && ok; id += unit_stride) {
+            for (int slot = first_unit; ok; slot += unit_stride) {
+                const int id = schedule_unit(slot, first_unit, unit_stride, causal);
+                if (id >= num_units) break;
                 const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
                 ok = mbar_wait(guard, q_empty, q_ph ^ 1u, 0x1400u);
                 if (!ok) break;
@@ -198,7 +200,9 @@ fa_fwd_pers_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
                 return __all_sync(0xffffffffu, mbar_wait(guard, bar, parity, site));
             };
 
-            for (int id = first_unit; id < num_units && ok; id += unit_stride) {
+            for (int slot = first_unit; ok; slot += unit_stride) {
+                const int id = schedule_unit(slot, first_unit, unit_stride, causal);
+                if (id >= num_units) break;
                 const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
                 ok = wait(q_full, q_ph, 0x1200u);
                 if (!ok) break;
@@ -283,7 +287,9 @@ fa_fwd_pers_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
         uint32_t s_count = 0;                          // completions of s_full[i] consumed so far
         uint32_t units_done = 0;                       // completions of o_final[i] consumed so far
         bool ok = true;
-        for (int id = first_unit; id < num_units && ok; id += unit_stride) {
+        for (int slot = first_unit; ok; slot += unit_stride) {
+            const int id = schedule_unit(slot, first_unit, unit_stride, causal);
+            if (id >= num_units) break;
             const UnitCoord u = unit_coord(id, q_pairs, heads, seq_q, seq_k, causal);
             const int n = i ? u.nblk[1] : u.nblk[0];
             if (n == 0) continue;

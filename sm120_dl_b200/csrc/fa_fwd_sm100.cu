@@ -138,14 +138,22 @@ int launch_fa_r4(const DeviceInfo* dev, const b200_fa_config& cfg, const void* q
     const long units = static_cast<long>(q_pairs) * heads * batch;
     if (units > 0x7fffffffL) return fail(B200_ESHAPE, "too many work units");
     int grid = dev->sm_count < units ? dev->sm_count : static_cast<int>(units);
-    if (causal && units > grid) {
-        // heaviest units of a head first, every grid-th unit per CTA: a grid coprime to the
-        // units per head gives every CTA every weight class equally often
+    // Causal units differ in weight.  With many units per CTA and long sequences a CTA takes them
+    // in pairs of one heavy and one light unit of a head, equal in total (mode 2); otherwise
+    // heaviest first with a grid coprime to the units per head, so that every CTA meets every
+    // weight class (mode 1).  Measured, mode 1 / mode 2 (ms): B2 H64 S4096 D128 0.516 / 0.486,
+    // B1 H32 S16384 2.33 / 1.77, but B1 H32 S8192 (7 units per CTA: pairs halve the granularity)
+    // 0.531 / 0.571 and B8 H32 S2048 D64 (8 units per head, the light ones one or two blocks
+    // long: with pairs every CTA is in its short units at the same time) 0.250 / 0.287.
+    int causal_mode = causal ? 1 : 0;
+    if (causal && units >= 12L * grid && q_pairs % 2 == 0 && q_pairs >= 16) {
+        causal_mode = 2;
+    } else if (causal && units > grid) {
         while (grid > 1 && gcd_int(grid, q_pairs) != 1) --grid;
     }
     const float scale_log2 = softmax_scale * 1.4426950408889634f;
     kernel<<<grid, kFaThreads, T::kSmemBytes, stream>>>(tq, tk, tv, to, n_dst, seq_q, seq_k, heads, q_pairs,
-                                                        static_cast<int>(units), scale_log2, causal ? 1 : 0,
+                                                        static_cast<int>(units), scale_log2, causal_mode,
                                                         dev->status);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(B200_ECUDA, "launch of %s failed: %s", cfg.name, cudaGetErrorString(e));
